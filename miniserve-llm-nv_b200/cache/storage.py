@@ -79,7 +79,9 @@ class CacheStorage:
                       for g in groups if isinstance(g.need, PagedLatentNeed)))
 
     def run_view(self, plan: RunCache, ctx: StepContext):
-        """The cache of one layer run for this step."""
+        """The cache of one layer run for this step (a tuple of views for a mixer made of several members)."""
+        if isinstance(plan, tuple):
+            return tuple(None if member is None else self.run_view(member, ctx) for member in plan)
         need = self.groups[plan.group].need
         if isinstance(need, PagedKVNeed):
             block_tables, slots = ctx.group_views[self.paged_index[plan.group]]

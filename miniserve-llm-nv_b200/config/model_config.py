@@ -170,7 +170,7 @@ class RotationConfig:
             scaling = tuple(_positive(scaling, key, where + "scaling.") for key in ("factor", "original", "fast", "slow"))
         config = cls(base=_positive(data, "base", where), dims=_integer(data, "dims"), scaling=scaling)
         if config.dims % 2:
-            raise ValueError(f"{where}dims {config.dims} is odd; the rotation pairs entry i with entry i + dims/2")
+            raise ValueError(f"{where}dims {config.dims} is odd; the rotation turns pairs of entries")
         if config.base == 1.0:
             raise ValueError(f"{where}base must differ from 1")
         return config
@@ -478,3 +478,211 @@ class ZozezenConfig:
         layers = [dict(type=layer.type, mixer=layer.mixer.to_dict(), mlp=None if layer.mlp is None else layer.mlp.to_dict())
                   for layer in self.layers]
         return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, norm=dict(eps=self.eps), layers=layers)
+
+
+# --------------------------------------------------------------------------- Kivurax
+
+
+@dataclass(frozen=True)
+class MatrixMemoryConfig:
+    """The matrix-memory mixer (mLSTM): ``heads`` heads with queries and keys of ``dim`` and values of ``vdim`` entries; the
+    log gates are soft-capped at ``gate_cap``."""
+
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "MatrixMemoryConfig":
+        return cls(heads=_integer(data, "heads"), dim=_integer(data, "dim"), vdim=_integer(data, "vdim"),
+                   gate_cap=_positive(data, "gate_cap", where))
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(heads=self.heads, dim=self.dim, vdim=self.vdim, gate_cap=self.gate_cap)
+
+
+@dataclass(frozen=True)
+class WindowAttentionConfig:
+    """Grouped-query attention over a sliding window of ``window`` keys whose values are its keys as projected, with a
+    sink in the softmax, a norm per query and key head and an interleaved rotation of the first ``rot.dims`` entries."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int
+    rot: RotationConfig
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "WindowAttentionConfig":
+        rot = _section(data, "rot", where)
+        if _count(rot, "dims", 0) == 0:
+            rotation = RotationConfig(base=_positive(rot, "base", where + "rot."), dims=0)
+        else:
+            rotation = RotationConfig.from_dict(rot, where + "rot.")
+        config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
+                     vdim=_integer(data, "vdim"), scale=_positive(data, "scale", where),
+                     window=_integer(_section(data, "mask", where), "size"), rot=rotation)
+        if config.heads % config.kv_heads:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")
+        if config.vdim != config.dim:
+            raise ValueError(f"{where}vdim {config.vdim} differs from dim {config.dim}, but the values are the keys")
+        if config.rot.dims > config.dim:
+            raise ValueError(f"{where}rot.dims {config.rot.dims} exceeds the head size dim {config.dim}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        rot = dict(base=self.rot.base, dims=self.rot.dims)
+        if self.rot.scaling is not None:
+            rot["scaling"] = self.rot.scaling_dict()
+        return dict(heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim, scale=self.scale,
+                    mask=dict(size=self.window), rot=rot)
+
+
+@dataclass(frozen=True)
+class LinearRecurrenceConfig:
+    """The gated linear recurrence (a real-gated linear recurrent unit behind a short convolution): ``width`` channels whose
+    two gates are block-diagonal maps in ``blocks`` equal parts; a causal convolution of ``conv`` taps."""
+
+    width: int
+    blocks: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "LinearRecurrenceConfig":
+        config = cls(width=_integer(data, "width"), blocks=_integer(data, "blocks"), conv=_integer(data, "conv"))
+        if config.width % config.blocks:
+            raise ValueError(f"{where}blocks {config.blocks} does not divide width {config.width}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(width=self.width, blocks=self.blocks, conv=self.conv)
+
+
+@dataclass(frozen=True)
+class SideBySideConfig:
+    """Two mixers that read the same input; the result is ``left_scale * left + right_scale * right``."""
+
+    left: WindowAttentionConfig
+    right: LinearRecurrenceConfig
+    left_scale: float
+    right_scale: float
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "SideBySideConfig":
+        return cls(left=WindowAttentionConfig.from_dict(_section(data, "left", where), where + "left."),
+                   right=LinearRecurrenceConfig.from_dict(_section(data, "right", where), where + "right."),
+                   left_scale=_number(data, "left_scale"), right_scale=_number(data, "right_scale"))
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(left=self.left.to_dict(), right=self.right.to_dict(), left_scale=self.left_scale, right_scale=self.right_scale)
+
+
+@dataclass(frozen=True)
+class DeltaRuleConfig:
+    """The gated delta rule: ``heads`` value heads of ``vdim`` entries over ``kv_heads`` query/key heads of ``dim`` entries;
+    queries, keys and values pass a causal convolution of ``conv`` taps."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "DeltaRuleConfig":
+        config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
+                     vdim=_integer(data, "vdim"), conv=_integer(data, "conv"))
+        if config.heads % config.kv_heads:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim, conv=self.conv)
+
+
+@dataclass(frozen=True)
+class KivuraxFeedForwardConfig:
+    """``kind`` "dense": a gated feed-forward of inner size ``ff`` whose three projections have biases.  ``kind`` "moe":
+    ``experts`` gated experts of inner size ``ff`` without biases, of which a token uses ``top``."""
+
+    kind: str
+    ff: int
+    experts: int = 0
+    top: int = 0
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "KivuraxFeedForwardConfig":
+        kind = data.get("kind")
+        if kind == "dense":
+            return cls(kind="dense", ff=_integer(data, "ff"))
+        if kind == "moe":
+            router = _section(data, "router", where)
+            config = cls(kind="moe", ff=_integer(_section(data, "expert", where), "ff"), experts=_integer(router, "experts"),
+                         top=_integer(router, "top"))
+            if config.top > config.experts:
+                raise ValueError(f"{where}router.top {config.top} exceeds router.experts {config.experts}")
+            return config
+        raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}kind {kind!r} is not implemented (dense, moe)")
+
+    def to_dict(self) -> dict[str, Any]:
+        if self.kind == "dense":
+            return dict(kind="dense", ff=self.ff)
+        return dict(kind="moe", expert=dict(ff=self.ff), router=dict(experts=self.experts, top=self.top))
+
+
+@dataclass(frozen=True)
+class KivuraxLayerConfig:
+    type: str       # "mlstm", "parallel" or "delta"
+    mixer: Any
+    mlp: Any        # KivuraxFeedForwardConfig or None
+
+
+@dataclass(frozen=True)
+class KivuraxConfig:
+    """The Kivurax decoder: ``config.json`` holds ``architecture``, ``vocab``, ``width``, ``norm.eps``, ``residual_mult`` and
+    ``layers``, a list whose entries give each layer's mixer ``type`` (``mlstm``, ``parallel`` or ``delta``), the mixer's
+    sizes and constants (``mixer``) and its feed-forward (``mlp``, or null).  Every size and constant is read."""
+
+    vocab: int
+    width: int
+    eps: float
+    residual_mult: float
+    layers: tuple
+    architecture: str = "Kivurax"
+
+    MIXERS = {"mlstm": MatrixMemoryConfig, "parallel": SideBySideConfig, "delta": DeltaRuleConfig}
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "KivuraxConfig":
+        if data.get("architecture") != "Kivurax":
+            raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: expected architecture 'Kivurax', got {data.get('architecture')!r}")
+        raw_layers = data.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ValueError("layers must be a non-empty list in the model config")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"layers[{index}]."
+            if not isinstance(raw, Mapping):
+                raise ValueError(f"layers[{index}] must be an object")
+            kind = raw.get("type")
+            if kind not in cls.MIXERS:
+                raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}type {kind!r} is not implemented "
+                                            f"({', '.join(cls.MIXERS)})")
+            mixer = cls.MIXERS[kind].from_dict(_section(raw, "mixer", where), where + "mixer.")
+            mlp = None if raw.get("mlp") is None else KivuraxFeedForwardConfig.from_dict(_section(raw, "mlp", where), where + "mlp.")
+            layers.append(KivuraxLayerConfig(kind, mixer, mlp))
+        mult = _number(data, "residual_mult")
+        if not math.isfinite(mult):
+            raise ValueError(f"residual_mult must be finite, got {mult}")
+        return cls(vocab=_integer(data, "vocab"), width=_integer(data, "width"),
+                   eps=_positive(_section(data, "norm", ""), "eps", "norm."), residual_mult=mult, layers=tuple(layers))
+
+    def to_dict(self) -> dict[str, Any]:
+        """The ``config.json`` content that reads back as this configuration."""
+        layers = [dict(type=layer.type, mixer=layer.mixer.to_dict(), mlp=None if layer.mlp is None else layer.mlp.to_dict())
+                  for layer in self.layers]
+        return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, norm=dict(eps=self.eps),
+                    residual_mult=self.residual_mult, layers=layers)

@@ -110,9 +110,14 @@ def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size
     from ..parts.base import PagedKVNeed, PagedLatentNeed
 
     chosen = []
+    pairs = []
     for index, run in enumerate(model.spec.order):
-        plan = model.run_caches[index]
-        mixer = model.blocks[run.layer].mixer
+        plan, mixer = model.run_caches[index], model.blocks[run.layer].mixer
+        if isinstance(plan, tuple):          # a mixer of several members, each with its own cache
+            pairs.extend(zip(plan, mixer.members))
+        else:
+            pairs.append((plan, mixer))
+    for plan, mixer in pairs:
         if plan is None or not plan.writable or plan.slot != 0:
             continue
         need = model.cache_groups[plan.group].need

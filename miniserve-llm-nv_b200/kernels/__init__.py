@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -155,31 +155,38 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                 _i(x.numel() // size), _i(size), _f(eps), _stream()))
 
 
-def postnorm_add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
-                         weight: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-    """``residual += post_weight * delta / rms(delta)`` (float32, in place), ``out = weight * residual / rms(residual)``: a
-    sublayer's output passes a norm of its own on its way into the stream, and the stream is normed for the next
-    sublayer.  With ``rows`` (int32 ``[K]``) only those rows are computed, into ``out [K, H]``, and the residual is left
-    untouched.  The weights may be float32 or bfloat16 whatever ``out`` is."""
+def postnorm_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
+                         post_eps: float, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+                         rows: Optional[torch.Tensor] = None, post_scale: float = 1.0) -> None:
+    """``residual += post_scale * post_weight * delta / rms(delta)`` (float32, in place), ``out = weight * residual /
+    rms(residual)``: a sublayer's output passes a norm of its own on its way into the stream, and the stream is normed for
+    the next sublayer.  ``delta`` None: nothing is added.  ``weight`` None: the stream is not normed, ``out`` is the stream
+    rounded once to ``out``'s type (a sublayer that reads the stream itself).  With ``rows`` (int32 ``[K]``) only those
+    rows are computed, into ``out [K, H]``, and the residual is left untouched.  The weights may be float32 or bfloat16
+    whatever ``out`` is."""
     hidden = residual.shape[1]
     n_out = residual.shape[0] if rows is None else rows.numel()
     _want(residual, "residual", torch.float32)
-    _want(delta, "delta", out.dtype, residual.shape)
     _want(out, "out", None, (n_out, hidden))
-    _want(post_weight, "post_weight", None, (hidden,))
-    _want(weight, "weight", None, (hidden,))
+    if delta is not None:
+        _want(delta, "delta", out.dtype, residual.shape)
+        _want(post_weight, "post_weight", None, (hidden,))
+    if weight is not None:
+        _want(weight, "weight", None, (hidden,))
     if rows is not None:
         _want(rows, "rows", torch.int32)
-    _check(library().ms_postnorm_add_rmsnorm(_ptr(residual), _ptr(delta), _i(_code(out.dtype)), _ptr(post_weight),
-                                             _i(_code(post_weight.dtype)), _f(post_eps), _ptr(weight), _i(_code(weight.dtype)),
-                                             _f(eps), _ptr(rows), _ptr(out), _i(n_out), _i(hidden), _stream()))
+    _check(library().ms_postnorm_add_rmsnorm(
+        _ptr(residual), _ptr(delta), _i(_code(out.dtype)), _ptr(post_weight) if delta is not None else None,
+        _i(_code(post_weight.dtype)) if delta is not None else 0, _f(post_eps), _f(post_scale), _ptr(weight),
+        _i(_code(weight.dtype)) if weight is not None else 0, _f(eps), _ptr(rows), _ptr(out), _i(n_out), _i(hidden), _stream()))
 
 
 def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int, n_kv: int, head_dim: int, value_dim: int,
                 slots: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                 cos_sin: Optional[torch.Tensor], rotary_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                q_out: torch.Tensor) -> None:
-    """Per-head RMSNorm of q and k, half-split rotation of their first ``rotary_dim`` entries, and the append of k and v
+                q_out: torch.Tensor, interleaved: bool = False) -> None:
+    """Per-head RMSNorm of q and k, rotation of their first ``rotary_dim`` entries (entry i with entry i + rotary_dim / 2,
+    or, ``interleaved``, entry 2i with entry 2i + 1), and the append of k and v
     to one layer's pools, for a projection ``proj [N, ld]`` whose columns are laid out freely: query head h at
     ``q_col + h * head_dim``, key head g at ``k_col + g * head_dim``, value head g at ``v_col + g * value_dim``.
     ``k_col < 0``: the projection holds no keys and values (the layer reads another layer's) and only ``q_out
@@ -209,7 +216,7 @@ def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int
         _ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(q_col), _i(k_col if own else -1), _i(v_col if own else -1), _i(n_q), _i(n_kv),
         _i(head_dim), _i(value_dim), _ptr(slots) if own else None, _ptr(q_weight), _ptr(k_weight) if own else None, _f(eps),
         _ptr(cos_sin), _i(rotary_dim), _ptr(k_pool) if own else None, _ptr(v_pool) if own else None,
-        _i(k_pool.shape[2]), _ptr(q_out), _i(n), _stream()))
+        _i(k_pool.shape[2]) if own else 1, _ptr(q_out), _i(n), _i(1 if interleaved else 0), _stream()))
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos_sin: torch.Tensor, magnitude: float = 1.0) -> None:
@@ -256,8 +263,9 @@ def qk_norm_rope_append(qkv: torch.Tensor, slots: torch.Tensor, q_weight: Option
         _i(n_q), _i(n_kv), _i(head_dim), _ptr(q_out), _i(n), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> None:
-    """``out[n, c] = silu(gate_up[n, c]) * gate_up[n, I + c]`` for gate_up ``[N, 2 I]``.
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False, bias: Optional[torch.Tensor] = None) -> None:
+    """``out[n, c] = silu(gate_up[n, c]) * gate_up[n, I + c]`` for gate_up ``[N, 2 I]``.  With ``bias`` (float32 ``[2 I]``,
+    not with ``paired``) it is added to both halves first, in float32.
 
     ``paired``: the columns come as :func:`interleave_gate_up` orders a weight's rows (eight gate columns, then
     the up columns of the same features, and so on): ``out[n, 8 j + r] = silu(gate_up[n, 16 j + r]) *
@@ -266,8 +274,29 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> 
     n, inter = out.shape
     _want(gate_up, "gate_up", None, (n, 2 * inter))
     _want(out, "out", gate_up.dtype)
+    if bias is not None:
+        _want(bias, "bias", torch.float32, (2 * inter,))
+        if paired:
+            raise KernelError("silu_mul: a bias goes with the plain layout (gate columns, then up columns)")
+        _check(library().ms_silu_mul_bias(_ptr(gate_up), _i(_code(gate_up.dtype)), _ptr(bias), _ptr(out), _i(n), _i(inter), _stream()))
+        return
     _check(library().ms_silu_mul(_ptr(gate_up), _i(_code(gate_up.dtype)), _ptr(out), _i(n), _i(inter),
                                  _i(1 if paired else 0), _stream()))
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """In place: ``x[n, c] += bias[c]`` (float32 ``[C]``), added in float32."""
+    _want(x, "x")
+    _want(bias, "bias", torch.float32, (x.shape[-1],))
+    _check(library().ms_add_bias(_ptr(x), _i(_code(x.dtype)), _ptr(bias), _i(x.numel() // x.shape[-1]), _i(x.shape[-1]), _stream()))
+
+
+def scaled_sum(a: torch.Tensor, a_scale: float, b: torch.Tensor, b_scale: float, out: torch.Tensor) -> None:
+    """``out = a_scale * a + b_scale * b`` elementwise, formed in float32; ``out`` may be ``a`` or ``b``."""
+    _want(a, "a")
+    _want(b, "b", a.dtype, a.shape)
+    _want(out, "out", a.dtype, a.shape)
+    _check(library().ms_scaled_sum(_ptr(a), _f(a_scale), _ptr(b), _f(b_scale), _ptr(out), _i(_code(a.dtype)), a.numel(), _stream()))
 
 
 # --------------------------------------------------------------------------- attention
@@ -633,20 +662,33 @@ def _state_rows(states: torch.Tensor, offset: int, length: int) -> int:
     return states.shape[1]
 
 
+CONV_ACTIVATIONS = {"none": 0, "silu": 1}
+
+
 def causal_conv_silu(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: torch.Tensor, states: torch.Tensor,
                      state_offset: int, state_slots: torch.Tensor, query_start: torch.Tensor, max_query_len: int,
                      out: torch.Tensor) -> None:
-    """Causal convolution per channel, then SiLU, over each request's tokens, continued from the request's state:
-    ``out[t, c] = silu(bias[c] + sum_k weight[c, k] * u[t - (taps - 1 - k), c])`` with ``u`` the columns ``col ..
-    col + channels`` of ``proj [N, ld]``; inputs before the portion come from ``states[slot, state_offset:]`` (float32
-    ``[taps - 1, channels]``, oldest first), which afterwards holds the last ``taps - 1`` inputs seen.  ``weight``
-    float32 ``[channels, taps]``, ``bias`` float32 ``[channels]``; ``state_slots`` int32 ``[R]``, ``query_start`` int32
-    ``[R + 1]``; ``out`` float32 ``[N, channels]``."""
+    """:func:`causal_conv` with a bias and SiLU."""
+    causal_conv(proj, col, weight, bias, states, state_offset, state_slots, query_start, max_query_len, out)
+
+
+def causal_conv(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: Optional[torch.Tensor], states: torch.Tensor,
+                state_offset: int, state_slots: torch.Tensor, query_start: torch.Tensor, max_query_len: int,
+                out: torch.Tensor, activation: str = "silu", in_bias: Optional[torch.Tensor] = None) -> None:
+    """Causal convolution per channel, then the activation (``"silu"`` or ``"none"``), over each request's tokens, continued
+    from the request's state: ``out[t, c] = act(bias[c] + sum_k weight[c, k] * u[t - (taps - 1 - k), c])`` with ``u`` the
+    columns ``col .. col + channels`` of ``proj [N, ld]`` (plus ``in_bias[c]``, float32 ``[channels]``: the bias of the
+    projection that made them; the zeros before a sequence's start do not get it); inputs before the portion come from
+    ``states[slot, state_offset:]`` (float32 ``[taps - 1, channels]``, oldest first), which afterwards holds the last
+    ``taps - 1`` inputs seen.  ``weight`` float32 ``[channels, taps]``, ``bias`` float32 ``[channels]`` or None;
+    ``state_slots`` int32 ``[R]``, ``query_start`` int32 ``[R + 1]``; ``out`` float32 ``[N, channels]``."""
     n, ld = proj.shape
     channels, taps = weight.shape
     _want(proj, "proj")
     _want(weight, "weight", torch.float32)
-    _want(bias, "bias", torch.float32, (channels,))
+    for name, tensor in (("bias", bias), ("in_bias", in_bias)):
+        if tensor is not None:
+            _want(tensor, name, torch.float32, (channels,))
     _want(out, "out", torch.float32, (n, channels))
     n_requests = state_slots.numel()
     _want(state_slots, "state_slots", torch.int32)
@@ -654,9 +696,10 @@ def causal_conv_silu(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: t
     if col < 0 or col + channels > ld or not 1 <= taps <= MAX_CONV_TAPS:
         raise KernelError(f"causal_conv_silu: {channels} channels from column {col} of rows of {ld}, {taps} taps")
     stride = _state_rows(states, state_offset, (taps - 1) * channels)
-    _check(library().ms_causal_conv_silu(_ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(col), _i(channels), _i(taps), _ptr(weight),
-                                         _ptr(bias), _ptr(states), stride, _i(state_offset), _ptr(state_slots), _ptr(query_start),
-                                         _i(n_requests), _i(max_query_len), _ptr(out), _stream()))
+    _check(library().ms_causal_conv(_ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(col), _i(channels), _i(taps), _ptr(weight),
+                                    _ptr(bias), _ptr(in_bias), _i(CONV_ACTIVATIONS[activation]), _ptr(states), stride,
+                                    _i(state_offset), _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(max_query_len),
+                                    _ptr(out), _stream()))
 
 
 def selective_scan(conv: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
@@ -704,6 +747,153 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col: int, weight: to
                                          _i(groups), _i(inner), _f(eps), _ptr(out), _i(n), _stream()))
 
 
+# --------------------------------------------------------------------------- recurrences that carry a matrix or a vector
+
+MAX_MATRIX_SCAN_DIM = 512     # entries of a query or key that matrix_scan spreads over a warp (32 lanes x 16)
+MATRIX_SCAN_MODES = {"memory": 0, "delta": 1}
+HEAD_GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
+
+
+def small_linear_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out[n, r] = sum_c x[n, c] weight[r, c] + bias[r]`` in float32 for a float32 weight of few rows (gate logits of a
+    recurrence: what the router's logits are to a mixture); ``x`` in the compute type, ``out`` float32 ``[N, R]``."""
+    n, width = x.shape
+    rows = weight.shape[0]
+    _want(x, "x")
+    _want(weight, "weight", torch.float32, (rows, width))
+    if bias is not None:
+        _want(bias, "bias", torch.float32, (rows,))
+    _want(out, "out", torch.float32, (n, rows))
+    _check(library().ms_small_linear_f32(_ptr(x), _i(_code(x.dtype)), _ptr(weight), _ptr(bias), _i(width), _i(rows), _ptr(out),
+                                         _i(n), _stream()))
+
+
+def unit_norm_heads(x: torch.Tensor, col: int, heads: int, dim: int, eps: float, scale: float) -> None:
+    """In place on float32 ``x [N, ld]``: head j's entries (columns ``col + j dim ..``) become ``scale * v / sqrt(sum v^2 +
+    eps)``."""
+    _want(x, "x", torch.float32)
+    if x.dim() != 2 or col < 0 or col + heads * dim > x.shape[1]:
+        raise KernelError(f"unit_norm_heads: {heads} heads of {dim} from column {col} of {tuple(x.shape)}")
+    _check(library().ms_unit_norm_heads(_ptr(x), _i(x.shape[1]), _i(col), _i(heads), _i(dim), _f(eps), _f(scale), _i(x.shape[0]),
+                                        _stream()))
+
+
+def exponential_gates(logits: torch.Tensor, cap: float, states: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
+                      query_start: torch.Tensor, max_query_len: int, gates: torch.Tensor) -> None:
+    """The gates of a matrix memory with exponential gating, stabilised by a running maximum that the request carries.
+    ``logits`` float32 ``[N, 2 H]`` = ``[input | forget]``; ``i = cap tanh(x / cap)``, ``f = logsigmoid(cap tanh(x / cap))``;
+    ``m_t = max(f_t + m_(t-1), i_t)`` from ``states[slot, state_offset + head]`` (which receives the last ``m``);
+    ``gates [N, H, 3]`` = ``(exp(f_t + m_(t-1) - m_t), exp(i_t - m_t), exp(-m_t))``."""
+    n, heads = gates.shape[0], gates.shape[1]
+    _want(logits, "logits", torch.float32, (n, 2 * heads))
+    _want(gates, "gates", torch.float32, (n, heads, 3))
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    stride = _state_rows(states, state_offset, heads)
+    _check(library().ms_exponential_gates(_ptr(logits), _f(cap), _ptr(states), stride, _i(state_offset), _ptr(state_slots),
+                                          _ptr(query_start), _i(n_requests), _i(heads), _ptr(gates), _stream()))
+
+
+def decay_gates(logits: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, gates: torch.Tensor) -> None:
+    """The gates of the delta rule: ``logits`` float32 ``[N, 2 H]`` = ``[b | a]``; ``gates [N, H, 2]`` = ``(exp(-exp(a_log)
+    softplus(a + dt_bias)), sigmoid(b))``."""
+    n, heads = gates.shape[0], gates.shape[1]
+    _want(logits, "logits", torch.float32, (n, 2 * heads))
+    _want(gates, "gates", torch.float32, (n, heads, 2))
+    _want(a_log, "a_log", torch.float32, (heads,))
+    _want(dt_bias, "dt_bias", torch.float32, (heads,))
+    _check(library().ms_decay_gates(_ptr(logits), _ptr(a_log), _ptr(dt_bias), _ptr(gates), _i(n), _i(heads), _stream()))
+
+
+def matrix_scan(mode: str, q: torch.Tensor, q_col: int, k: torch.Tensor, k_col: int, v: torch.Tensor, v_col: int,
+                gates: torch.Tensor, states: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
+                query_start: torch.Tensor, max_query_len: int, heads: int, kv_heads: int, dim: int, vdim: int, y: torch.Tensor,
+                q_scale: float = 1.0, bottom: Optional[torch.Tensor] = None) -> None:
+    """A recurrence that carries a ``dim x vdim`` matrix ``S`` per head, walked over each request's tokens from and into the
+    request's state.  Queries and keys of head j are the columns ``q_col + (j // (heads / kv_heads)) dim ..`` of ``q`` (and
+    ``k``), its values the columns ``v_col + j vdim ..`` of ``v`` (``q``, ``k``, ``v``: one 2-d tensor, float32 or the compute
+    type; the queries are multiplied by ``q_scale``).
+
+    ``"memory"``: ``gates [N, H, 3]`` = (keep, write, floor); ``S = keep S + write k v^T``, ``n = keep n + write k``, ``y = S^T q``
+    and ``bottom [N, H] = max(|n . q|, floor) + 1e-6``.  The state holds ``[H, vdim + 1, dim]``: the columns of ``S``, then ``n``.
+    ``"delta"``: ``gates [N, H, 2]`` = (decay, beta); ``S = decay S``, ``u = beta (v - S^T k)``, ``S = S + k u^T``, ``y = S^T q``.
+    The state holds ``[H, vdim, dim]``.  ``y`` float32 ``[N, H, vdim]``."""
+    code = MATRIX_SCAN_MODES[mode]
+    n = y.shape[0]
+    for name, tensor in (("q", q), ("k", k), ("v", v)):
+        _want(tensor, name)
+        if tensor.dim() != 2 or tensor.shape[0] != n or tensor.dtype != q.dtype:
+            raise KernelError(f"matrix_scan: {name} {tuple(tensor.shape)} {tensor.dtype} for {n} tokens")
+    if (heads % kv_heads or q_col < 0 or k_col < 0 or v_col < 0 or q_col + kv_heads * dim > q.shape[1]
+            or k_col + kv_heads * dim > k.shape[1] or v_col + heads * vdim > v.shape[1] or not 1 <= dim <= MAX_MATRIX_SCAN_DIM):
+        raise KernelError(f"matrix_scan: {heads}/{kv_heads} heads of {dim}/{vdim} at columns {q_col}, {k_col}, {v_col}")
+    _want(gates, "gates", torch.float32, (n, heads, 3 if code == 0 else 2))
+    _want(y, "y", torch.float32, (n, heads, vdim))
+    if code == 0:
+        _want(bottom, "bottom", torch.float32, (n, heads))
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    columns = vdim + 1 if code == 0 else vdim
+    stride = _state_rows(states, state_offset, heads * columns * dim)
+    _check(library().ms_matrix_scan(_i(code), _ptr(q), _i(q.shape[1]), _i(q_col), _ptr(k), _i(k.shape[1]), _i(k_col), _ptr(v),
+                                    _i(v.shape[1]), _i(v_col), _i(_code(q.dtype)), _f(q_scale), _ptr(gates), _ptr(states), stride,
+                                    _i(state_offset), _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(max_query_len),
+                                    _i(heads), _i(kv_heads), _i(dim), _i(vdim), _ptr(y), _ptr(bottom), _stream()))
+
+
+def head_norm_gate(y: torch.Tensor, bottom: Optional[torch.Tensor], weight: torch.Tensor, gate: torch.Tensor, gate_col: int,
+                   activation: str, eps: float, out: torch.Tensor) -> None:
+    """``v = y / bottom`` (per token and head; ``bottom`` None: ``y`` itself), each head divided by its root mean square
+    (``eps`` inside the root), times ``weight`` (float32: ``[H * vdim]``, or ``[vdim]`` shared by the heads), times
+    ``act(gate[n, gate_col + j])`` with ``act`` ``"sigmoid"`` or ``"silu"``.  ``y`` float32 ``[N, H, vdim]``; ``gate`` and ``out [N, H *
+    vdim]`` in the compute type."""
+    n, heads, vdim = y.shape
+    _want(y, "y", torch.float32)
+    if bottom is not None:
+        _want(bottom, "bottom", torch.float32, (n, heads))
+    _want(weight, "weight", torch.float32)
+    if weight.numel() not in (vdim, heads * vdim):
+        raise KernelError(f"head_norm_gate: a weight of {weight.numel()} numbers for {heads} heads of {vdim}")
+    _want(gate, "gate")
+    _want(out, "out", gate.dtype, (n, heads * vdim))
+    if gate.dim() != 2 or gate.shape[0] != n or gate_col < 0 or gate_col + heads * vdim > gate.shape[1]:
+        raise KernelError(f"head_norm_gate: gate {tuple(gate.shape)} from column {gate_col} for {heads} heads of {vdim}")
+    _check(library().ms_head_norm_gate(_ptr(y), _ptr(bottom), _ptr(weight), _i(1 if weight.numel() == heads * vdim and heads > 1 else 0),
+                                       _ptr(gate), _i(_code(gate.dtype)), _i(gate.shape[1]), _i(gate_col),
+                                       _i(HEAD_GATE_ACTIVATIONS[activation]), _f(eps), _ptr(out), _i(n), _i(heads), _i(vdim), _stream()))
+
+
+def gated_recurrence_scan(u: torch.Tensor, pre: torch.Tensor, gate_bias: torch.Tensor, rate: torch.Tensor, proj: torch.Tensor,
+                          y_col: int, y_bias: Optional[torch.Tensor], states: torch.Tensor, state_offset: int,
+                          state_slots: torch.Tensor, query_start: torch.Tensor, max_query_len: int, out: torch.Tensor) -> None:
+    """The real-gated linear recurrence per channel over each request's tokens, from and into the request's state:
+    ``r = sigmoid(pre[0] + gate_bias[0])``, ``i = sigmoid(pre[1] + gate_bias[1])``, ``log a = rate r``, ``S = a S + sqrt(1 - a^2)
+    i u``, and ``out = S gelu_tanh(proj[:, y_col + c] + y_bias[c])``.  ``u`` float32 ``[N, W]``, ``pre`` float32 ``[2, N, W]``,
+    ``gate_bias`` float32 ``[2, W]``, ``rate`` float32 ``[W]`` (negative), ``states[slot, state_offset:]`` float32 ``[W]``; ``out [N,
+    W]`` in ``proj``'s type."""
+    n, width = u.shape
+    _want(u, "u", torch.float32)
+    _want(pre, "pre", torch.float32, (2, n, width))
+    _want(gate_bias, "gate_bias", torch.float32, (2, width))
+    _want(rate, "rate", torch.float32, (width,))
+    _want(proj, "proj")
+    if y_bias is not None:
+        _want(y_bias, "y_bias", torch.float32, (width,))
+    _want(out, "out", proj.dtype, (n, width))
+    if proj.dim() != 2 or proj.shape[0] != n or y_col < 0 or y_col + width > proj.shape[1]:
+        raise KernelError(f"gated_recurrence_scan: {width} channels from column {y_col} of {tuple(proj.shape)}")
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    stride = _state_rows(states, state_offset, width)
+    _check(library().ms_gated_recurrence_scan(_ptr(u), _ptr(pre), _ptr(gate_bias), _ptr(rate), _ptr(proj), _i(_code(proj.dtype)),
+                                              _i(proj.shape[1]), _i(y_col), _ptr(y_bias), _ptr(states), stride, _i(state_offset),
+                                              _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(max_query_len), _i(width),
+                                              _ptr(out), _stream()))
+
+
 # --------------------------------------------------------------------------- routed experts
 
 
@@ -719,10 +909,11 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     further rows of ``weight`` only ride along in the product and leave their logits in ``logits``); the choice goes by
     ``score + correction`` (float32 ``[choose_from]`` or None) among the members of the ``groups[1]`` best of
     ``groups[0]`` equal groups of neighbours (a group's score: its largest choice score), and ``weights`` are the chosen
-    outputs' scores as they are."""
+    outputs' scores as they are.  ``scoring="sigmoid"``: the same with ``sigmoid(logit)`` of every output on its own as its
+    score."""
     n, width = x.shape
     experts = weight.shape[0]
-    if scoring == "all_softmax":
+    if scoring in ("all_softmax", "sigmoid"):
         total = experts if choose_from is None else choose_from
         if logits is None:
             logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)
@@ -737,7 +928,7 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         _want(weights, "weights", torch.float32, (n, top))
         _check(library().ms_router_choose(_ptr(x), _i(_code(x.dtype)), _ptr(weight), _ptr(bias), _i(width), _i(experts), _i(total),
                                           _i(top), _ptr(correction), _i(groups[0]), _i(groups[1]), _ptr(logits), _ptr(ids),
-                                          _ptr(weights), _i(n), _stream()))
+                                          _ptr(weights), _i(n), _i(1 if scoring == "sigmoid" else 0), _stream()))
         return
     if scoring != "chosen_softmax" or correction is not None or tuple(groups) != (1, 1) or choose_from not in (None, experts):
         raise KernelError("router_topk: a correction, groups and rows that ride along need scoring='all_softmax'")
@@ -765,17 +956,20 @@ def expert_route(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: 
     _check(library().ms_expert_route(_ptr(ids), _i(pairs), _i(experts), _ptr(offsets), _ptr(order), _ptr(place), _stream()))
 
 
-EXPERT_ACTIVATIONS = {"none": 0, "relu_square": 1, "clamped_glu": 2}
+EXPERT_ACTIVATIONS = {"none": 0, "relu_square": 1, "clamped_glu": 2, "silu_glu": 3}
 
 
 def expert_linear(x: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, out: torch.Tensor,
-                  offsets: torch.Tensor, relu_square: bool = False, activation: str = "none", limit: float = 0.0) -> None:
+                  offsets: torch.Tensor, relu_square: bool = False, activation: str = "none", limit: float = 0.0,
+                  pair_scale: Optional[torch.Tensor] = None) -> None:
     """One product per expert over its segment of the sorted pairs: ``out[i] = act(x[src(i)] @ weight[e]^T)`` for every
     place ``i`` of expert ``e``'s segment, ``weight [E, N, K]``, ``out [pairs, N]``.  With ``order`` the rows are gathered from
     the tokens (``src(i) = order[i] // top``, ``x [tokens, K]``), without it ``x [pairs, K]`` is in sorted order already.
     ``activation``: ``"relu_square"`` (or ``relu_square=True``): ``act(z) = max(z, 0)^2``; ``"clamped_glu"``: the rows of
     ``weight[e]`` alternate (gate row j, up row j) and ``out [pairs, N / 2]`` receives ``g sigmoid(1.702 g) (u + 1)`` with
-    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``.  ``offsets`` may bound more segments than ``weight`` has
+    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``; ``"silu_glu"``: the same layout, ``out`` receives
+    ``silu(s gate) (s up)`` where ``s`` is the pair's entry of ``pair_scale`` (float32 ``[tokens, top]``, needs ``order``; 1
+    without it): the expert computed on ``s`` times its input.  ``offsets`` may bound more segments than ``weight`` has
     experts (identity experts, sorted behind the others): their rows are left alone."""
     experts, n, k = weight.shape
     pairs = out.shape[0]
@@ -784,7 +978,13 @@ def expert_linear(x: torch.Tensor, order: Optional[torch.Tensor], top: int, weig
     code = EXPERT_ACTIVATIONS[activation]
     _want(x, "x", None)
     _want(weight, "weight", x.dtype)
-    _want(out, "out", x.dtype, (pairs, n // 2 if code == 2 else n))
+    _want(out, "out", x.dtype, (pairs, n // 2 if code >= 2 else n))
+    if pair_scale is not None:
+        if code != 3 or order is None:
+            raise KernelError("expert_linear: a scale per pair goes with 'silu_glu' and rows gathered through `order`")
+        _want(pair_scale, "pair_scale", torch.float32)
+        if pair_scale.numel() != pairs:
+            raise KernelError(f"expert_linear: {pair_scale.numel()} scales for {pairs} pairs")
     _want(offsets, "offsets", torch.int32)
     if offsets.numel() < experts + 1:
         raise KernelError(f"expert_linear: {offsets.numel()} offsets for {experts} experts")
@@ -794,21 +994,24 @@ def expert_linear(x: torch.Tensor, order: Optional[torch.Tensor], top: int, weig
         _want(order, "order", torch.int32, (pairs,))
     _check(library().ms_expert_linear(_ptr(x), _i(_code(x.dtype)), _i(k), _ptr(order), _i(top), _ptr(weight), _ptr(out),
                                       _i(out.shape[1]), _ptr(offsets), _i(experts), _i(pairs), _i(n), _i(k), _i(code), _f(limit),
-                                      _stream()))
+                                      _ptr(pair_scale), _stream()))
 
 
-def expert_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
+def expert_combine(y: torch.Tensor, place: torch.Tensor, weights: Optional[torch.Tensor], shared: Optional[torch.Tensor],
                    out: torch.Tensor, ids: Optional[torch.Tensor] = None, first_identity: int = 0,
                    x: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None, shared_gate_col: int = 0) -> None:
     """``out[n] = sum_k weights[n, k] * y[place[n * top + k]] (+ shared[n])``, summed in float32 in the order of k.
     With ``ids`` (int32 ``[N, top]``) a choice whose id is ``first_identity`` or more is an identity expert and adds
     ``weights[n, k] * x[n]`` instead.  With ``shared_gate`` (float32 ``[N, ld]``) the shared expert's output is multiplied
-    by ``sigmoid(shared_gate[n, shared_gate_col])``."""
-    n, top = weights.shape
+    by ``sigmoid(shared_gate[n, shared_gate_col])``.  ``weights`` None: every weight is 1 (the experts' inputs carried
+    them)."""
     width = out.shape[1]
+    n = out.shape[0]
+    top = place.numel() // max(n, 1) if weights is None else weights.shape[1]
     _want(y, "y", out.dtype, (n * top, width))
     _want(place, "place", torch.int32, (n * top,))
-    _want(weights, "weights", torch.float32)
+    if weights is not None:
+        _want(weights, "weights", torch.float32, (n, top))
     _want(out, "out", None, (n, width))
     if shared is not None:
         _want(shared, "shared", out.dtype, (n, width))

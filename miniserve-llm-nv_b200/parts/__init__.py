@@ -1,6 +1,7 @@
 """Layer parts and the model assembled from them."""
 
-from . import attention, block, experts, feed_forward, latent_attention, norm, position, state_space  # noqa: F401  (register the built-in parts)
+from . import (attention, block, experts, feed_forward, latent_attention, linear_recurrence, matrix_memory, norm, position,
+               side_by_side, state_space)  # noqa: F401  (register the built-in parts)
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PAGED_NEEDS, POSITIONS, FoldedInput, NormFold, PagedKVNeed, PagedLatentNeed, PostNormed,
                    ResidualAdd, ParamSpec, Part, StateNeed,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)

@@ -20,7 +20,8 @@ output projection then reads ``num_heads * value_dim`` numbers), ``sink`` (the s
 term, ``exp(0)``: a key of score 0 that has no value, so a head can attend to nothing), ``output_gate`` (head h's
 output is multiplied by ``sigmoid(W_g x)_h``, one number per head, from the same input as the projections) and
 ``own_kv=False`` (the layer has no key and value tensors: its run reads another run's cache, ``LayerRun.cache_of``,
-with its own queries).  With any of them the projections (queries, keys and values if the layer has them, gate
+with its own queries) and ``values_from_keys`` (the layer has no value tensor: a token's values are its keys as
+projected, before their norm and rotation).  With any of them the projections (queries, keys and values if the layer has them, gate
 logits) are one product over a row-concatenated weight padded with zero rows to a multiple of eight, followed by
 ``kernels.qkv_prepare`` (per-head norm, rotation, append) and ``kernels.paged_attention`` with the sink and the gate
 applied as it stores.
@@ -47,10 +48,11 @@ class Attention(Part):
                  q_name: str = "q_proj.weight", k_name: str = "k_proj.weight",
                  v_name: str = "v_proj.weight", o_name: str = "o_proj.weight", q_norm_name: str = "q_norm.weight",
                  k_norm_name: str = "k_norm.weight", value_dim: Optional[int] = None, sink: bool = False,
-                 output_gate: bool = False, own_kv: bool = True, gate_name: str = "g_proj.weight") -> None:
+                 output_gate: bool = False, own_kv: bool = True, gate_name: str = "g_proj.weight",
+                 values_from_keys: bool = False) -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
-        general_form = bool(sink or output_gate or not own_kv or (value_dim is not None and value_dim != head_dim))
+        general_form = bool(sink or output_gate or not own_kv or values_from_keys or (value_dim is not None and value_dim != head_dim))
         if general_form and 1 <= head_dim <= kernels.MAX_HEAD_DIM:
             pass            # (the general form's kernels take odd head sizes too; the rotation checks its own size)
         elif head_dim % 2 or not 2 <= head_dim <= kernels.MAX_HEAD_DIM:
@@ -75,18 +77,21 @@ class Attention(Part):
         self.sink, self.output_gate, self.own_kv = bool(sink), bool(output_gate), bool(own_kv)
         # the general form: one product for all projections of the input, then qkv_prepare and the general call of
         # paged_attention (the fast paths below are written for plain heads of one size)
-        self.general = self.sink or self.output_gate or not self.own_kv or self.value_dim != head_dim
+        self.values_from_keys = bool(values_from_keys)
+        if self.values_from_keys and (self.value_dim != head_dim or not self.own_kv):
+            raise ValueError("values_from_keys: the values are the layer's own keys, so both have the same size")
+        self.general = self.sink or self.output_gate or not self.own_kv or self.values_from_keys or self.value_dim != head_dim
         if self.general and (self.score_softcap or self.score_bias_slopes is not None):
             raise ValueError("score modifiers are not implemented together with value_dim, sink, output_gate or own_kv=False")
-        if self.general and getattr(self.position, "interleaved", False):
-            raise ValueError("value_dim, sink, output_gate and own_kv=False are implemented for the half-split rotation")
         self.names = dict(q=prefix + q_name, k=prefix + k_name, v=prefix + v_name, o=prefix + o_name,
                           q_norm=prefix + q_norm_name, k_norm=prefix + k_norm_name, g=prefix + gate_name)
         # columns of the general form's projection: queries, keys, values, gate logits, zero padding
         q_rows = num_heads * head_dim
-        kv_rows = num_kv_heads * (head_dim + self.value_dim) if self.own_kv else 0
+        kv_rows = num_kv_heads * (head_dim + (0 if self.values_from_keys else self.value_dim)) if self.own_kv else 0
         self.k_col = q_rows if self.own_kv else -1
         self.v_col = q_rows + num_kv_heads * head_dim if self.own_kv else -1
+        if self.values_from_keys:
+            self.v_col = self.k_col            # the value columns ARE the key columns, read before norm and rotation
         self.gate_col = q_rows + kv_rows if self.output_gate else -1
         self.in_rows = (q_rows + kv_rows + (num_heads if self.output_gate else 0) + 7) // 8 * 8
         self.qkv_weight: Optional[torch.Tensor] = None
@@ -99,7 +104,9 @@ class Attention(Part):
         h, d, dv = self.hidden_size, self.head_dim, self.value_dim
         specs = [ParamSpec(self.names["q"], (self.num_heads * d, h))]
         if self.own_kv:
-            specs += [ParamSpec(self.names["k"], (self.num_kv_heads * d, h)), ParamSpec(self.names["v"], (self.num_kv_heads * dv, h))]
+            specs.append(ParamSpec(self.names["k"], (self.num_kv_heads * d, h)))
+            if not self.values_from_keys:
+                specs.append(ParamSpec(self.names["v"], (self.num_kv_heads * dv, h)))
         if self.qk_norm:
             specs.append(ParamSpec(self.names["q_norm"], (d,), "vector"))
             if self.own_kv:
@@ -116,7 +123,9 @@ class Attention(Part):
         n = self.names
         self.o_weight = tensors[n["o"]]
         if self.general:
-            pieces = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
+            pieces = [tensors[n["q"]]] + ([tensors[n["k"]]] if self.own_kv else [])
+            if self.own_kv and not self.values_from_keys:
+                pieces.append(tensors[n["v"]])
             if self.output_gate:
                 pieces.append(tensors[n["g"]])
             padding = self.in_rows - sum(p.shape[0] for p in pieces)
@@ -201,10 +210,11 @@ class Attention(Part):
             raise RuntimeError("a layer with keys and values of its own writes its cache; a layer without reads another run's")
         proj = ctx.buffer("attention.proj", (n, self.in_rows), x.dtype)
         kernels.linear(x, self.qkv_weight, proj)
-        cos_sin, rotary_dim, _ = self.position.fused_args(ctx)
+        cos_sin, rotary_dim, interleaved = self.position.fused_args(ctx)
         q = ctx.buffer("attention.q", (n, n_q, d), x.dtype)
         kernels.qkv_prepare(proj, 0, self.k_col, self.v_col, n_q, n_kv, d, dv, cache.slots, self.q_norm_weight,
-                            self.k_norm_weight, self.eps, cos_sin, rotary_dim, cache.key_pool, cache.value_pool, q)
+                            self.k_norm_weight, self.eps, cos_sin, rotary_dim, cache.key_pool, cache.value_pool, q,
+                            interleaved=interleaved)
         attended = ctx.buffer("attention.attended", (n, n_q, dv), x.dtype)
         kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
                                 ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,

@@ -12,7 +12,8 @@ norm            ``add_and_norm(residual, delta, out, rows=None)``: add ``delta``
                 into the float32 residual stream in place, write the norm of the sum to ``out``
 position        ``tables(ctx)``: per-step device tables for the rotation; ``fused_args()``
 mixer           ``forward(x, ctx, cache) -> y``; ``cache_need()`` says what ``cache`` must be (paged keys
-                and values, paged latent vectors, a fixed-size state, or nothing)
+                and values, paged latent vectors, a fixed-size state, nothing, or a tuple of these for a
+                mixer made of several: ``cache`` is then the tuple of their views)
 feed_forward    ``forward(x, ctx) -> y``
 block           ``forward(residual, delta, ctx, cache) -> delta``: arranges the four above
 ==============  ==========================================================================
@@ -113,12 +114,13 @@ class ResidualAdd:
 class PostNormed:
     """What a block hands on where a sublayer's output passes a norm of its own before it is added to the stream:
     ``x`` is the output as computed, ``weight`` and ``eps`` are that norm's (``weight * x / rms(x)`` is what the stream
-    receives).  The norm that reads the stream next carries out both in one kernel
-    (``kernels.postnorm_add_rmsnorm``)."""
+    receives, times ``scale`` where a design damps what its sublayers add).  The norm that reads the stream next carries
+    out both in one kernel (``kernels.postnorm_add_rmsnorm``)."""
 
     x: torch.Tensor
     weight: torch.Tensor
     eps: float
+    scale: float = 1.0
 
 
 @dataclass

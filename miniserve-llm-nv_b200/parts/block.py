@@ -125,14 +125,18 @@ class ParallelBlock:
 @register_block("sandwich")
 class SandwichBlock:
     """``x <- x + post_1(mixer(norm_1(x)))``, then ``x <- x + post_2(feed_forward(norm_2(x)))``: every sublayer has a
-    norm before it and a norm of its own output.  A layer may have no feed-forward.
+    norm before it and a norm of its own output.  A layer may have no feed-forward.  With ``residual_scale`` m what a sublayer adds is
+    ``m * post(...)``; with ``identity`` parts as ``norm_1`` and ``norm_2`` the sublayers read the stream itself, which is the
+    arrangement that norms a sublayer's output only: ``x <- x + m * post_1(mixer(x))``.
 
     A sublayer's output is handed on unadded together with its output norm (:class:`~.base.PostNormed`); the norm that
     reads the stream next (this block's second, the next block's first, or the model's last) norms the output, adds it
     to the float32 stream and norms the stream in one kernel.
     """
 
-    def __init__(self, *, mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_post_norm, feed_forward_post_norm=None) -> None:
+    def __init__(self, *, mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_post_norm, feed_forward_post_norm=None,
+                 residual_scale: float = 1.0) -> None:
+        self.residual_scale = float(residual_scale)
         if (feed_forward is None) != (feed_forward_norm is None) or (feed_forward is None) != (feed_forward_post_norm is None):
             raise ValueError("a sandwich block has a feed-forward with both of its norms, or none of the three")
         self.mixer, self.feed_forward = mixer, feed_forward
@@ -148,9 +152,9 @@ class SandwichBlock:
             raise TypeError("a sandwich block takes its input from its own norm")
         normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)
         self.mixer_norm.add_and_norm(residual, pending, normed)
-        mixed = PostNormed(self.mixer.forward(normed, ctx, cache), *self.mixer_post_norm.fold())
+        mixed = PostNormed(self.mixer.forward(normed, ctx, cache), *self.mixer_post_norm.fold(), self.residual_scale)
         if self.feed_forward is None:
             return mixed
         normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)      # (the mixer has read the first)
         self.feed_forward_norm.add_and_norm(residual, mixed, normed)
-        return PostNormed(self.feed_forward.forward(normed, ctx), *self.feed_forward_post_norm.fold())
+        return PostNormed(self.feed_forward.forward(normed, ctx), *self.feed_forward_post_norm.fold(), self.residual_scale)

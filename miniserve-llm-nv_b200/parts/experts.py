@@ -12,7 +12,7 @@
 gate and an up projection, ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``, and
 ``y = g sigmoid(1.702 g) (u + 1)`` enters the down projection (the two weights are kept as one whose rows alternate,
 gate row j, up row j, so that one product's epilogue holds both).  The shared expert has the same form with
-``shared_limit``.
+``shared_limit``.  ``silu_glu``: ``y = silu(W_gate h) (W_up h)``, the same two weights kept the same way, no limit.
 
 Other ways to route, each off by default:
 
@@ -21,6 +21,11 @@ Other ways to route, each off by default:
   CHOICE only.
 * ``groups=(count, keep)``: the router's outputs form ``count`` equal groups of neighbours; a group's score is its
   largest choice score, and only members of the ``keep`` best groups can be chosen.
+* ``scoring="sigmoid"``: scores are ``sigmoid(z)`` of every router output on its own; the ``top`` largest are chosen (a tie
+  goes to the lower index) and a chosen expert's weight is its score as it is.
+* ``weight_on="input"``: the weight multiplies what the expert reads, not what it returns: the output is the sum of
+  ``expert(w h)`` over the chosen experts.  (An expert's first products are linear, so the factor is applied to their
+  float32 sums as the activation is formed.)
 * ``identity``: the last ``identity`` router outputs stand for experts without tensors whose output is their input.
 * ``shared_gate_name``: a ``[1, width]`` weight; the shared expert's output is multiplied by ``sigmoid(w . h)`` per
   token (the row rides along with the router's float32 product).
@@ -51,11 +56,15 @@ class RoutedExperts(Part):
                  shared_name: str = "shared.", up_name: str = "up", down_name: str = "down", gate_name: str = "gate",
                  limit: Optional[float] = None, shared_limit: Optional[float] = None, identity: int = 0,
                  scoring: str = "chosen_softmax", correction_name: Optional[str] = None, groups: tuple = (1, 1),
-                 shared_gate_name: Optional[str] = None) -> None:
-        if activation not in ("relu_square", "clamped_glu"):
-            raise ValueError(f"routed_experts implements the activations 'relu_square' and 'clamped_glu', not {activation!r}")
-        if scoring not in ("chosen_softmax", "all_softmax"):
-            raise ValueError(f"routed_experts scores by 'chosen_softmax' or 'all_softmax', not {scoring!r}")
+                 shared_gate_name: Optional[str] = None, weight_on: str = "output") -> None:
+        if activation not in ("relu_square", "clamped_glu", "silu_glu"):
+            raise ValueError(f"routed_experts implements the activations 'relu_square', 'clamped_glu' and 'silu_glu', not {activation!r}")
+        if scoring not in ("chosen_softmax", "all_softmax", "sigmoid"):
+            raise ValueError(f"routed_experts scores by 'chosen_softmax', 'all_softmax' or 'sigmoid', not {scoring!r}")
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"routed_experts weights an expert's 'output' or its 'input', not {weight_on!r}")
+        if weight_on == "input" and (activation != "silu_glu" or identity):
+            raise ValueError("weights on the experts' inputs are implemented for the 'silu_glu' activation without identity experts")
         total = experts + identity
         count, keep = (int(g) for g in groups)
         if identity < 0 or count < 1 or total % count or not 1 <= keep <= count:
@@ -64,12 +73,15 @@ class RoutedExperts(Part):
             raise ValueError(f"every token uses {top} of {total} experts ({keep} of {count} groups kept): not possible")
         if activation == "clamped_glu" and (limit is None or (shared_size and shared_limit is None)):
             raise ValueError("the clamped activation needs its limit (and the shared expert's)")
-        if (correction_name or (count, keep) != (1, 1)) and scoring != "all_softmax":
+        if activation == "silu_glu" and shared_size:
+            raise ValueError("a shared expert is not implemented for the 'silu_glu' activation")
+        if (correction_name or (count, keep) != (1, 1)) and scoring not in ("all_softmax", "sigmoid"):
             raise ValueError("a correction of the choice and groups are implemented for scoring='all_softmax'")
         self.prefix, self.hidden_size = prefix, hidden_size
         self.experts, self.top, self.expert_size, self.shared_size = experts, top, expert_size, shared_size
         self.identity, self.total, self.scoring, self.groups = identity, total, scoring, (count, keep)
-        self.gated = activation == "clamped_glu"
+        self.gated = activation in ("clamped_glu", "silu_glu")
+        self.activation, self.weight_on = activation, weight_on
         self.limit = float(limit) if limit is not None else 0.0
         self.shared_limit = float(shared_limit) if shared_limit is not None else 0.0
         self.router_bias = bool(router_bias)
@@ -149,7 +161,8 @@ class RoutedExperts(Part):
         # (the segments of identity experts lie behind those of the experts with tensors; their rows are not computed)
         hidden = ctx.buffer("experts.hidden", (pairs, self.expert_size), x.dtype)
         if self.gated:
-            kernels.expert_linear(x, order, top, self.up, hidden, offsets, activation="clamped_glu", limit=self.limit)
+            kernels.expert_linear(x, order, top, self.up, hidden, offsets, activation=self.activation, limit=self.limit,
+                                  pair_scale=weights if self.weight_on == "input" else None)
         else:
             kernels.expert_linear(x, order, top, self.up, hidden, offsets, activation="relu_square")
         results = ctx.buffer("experts.results", (pairs, width), x.dtype)
@@ -167,7 +180,7 @@ class RoutedExperts(Part):
             shared = ctx.buffer("experts.shared", (n, width), x.dtype)
             kernels.linear(shared_hidden, self.shared_down, shared)
         out = ctx.buffer("experts.out", (n, width), x.dtype)
-        kernels.expert_combine(results, place, weights, shared, out, ids=ids if self.identity else None,
+        kernels.expert_combine(results, place, None if self.weight_on == "input" else weights, shared, out, ids=ids if self.identity else None,
                                first_identity=self.experts, x=x if self.identity else None,
                                shared_gate=logits if self.names["shared_gate"] else None, shared_gate_col=self.total)
         return out

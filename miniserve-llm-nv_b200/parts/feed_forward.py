@@ -2,7 +2,9 @@
 (miniserve/model/layers.py:71-87) with ``silu`` as the activation; gate and up run as one
 matrix product over one weight that holds both.  Where the intermediate size is a multiple of eight
 the rows of the two alternate in blocks of eight (``kernels.interleave_gate_up``), which lets the
-product of a decode step apply the activation as it stores; else the up rows follow the gate rows."""
+product of a decode step apply the activation as it stores; else the up rows follow the gate rows.  With ``bias=True`` the
+three projections have biases (``down(act(gate(x) + b_g) * (up(x) + b_u)) + b_d``, added in float32 as the activation and
+the output are formed); the up rows then follow the gate rows."""
 
 from __future__ import annotations
 
@@ -19,23 +21,35 @@ from .context import StepContext
 class GatedMLP(Part):
     def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  gate_name: str = "gate_proj.weight", up_name: str = "up_proj.weight",
-                 down_name: str = "down_proj.weight") -> None:
+                 down_name: str = "down_proj.weight", bias: bool = False, gate_bias_name: str = "gate_proj.bias",
+                 up_bias_name: str = "up_proj.bias", down_bias_name: str = "down_proj.bias") -> None:
         if activation != "silu":
             raise ValueError(f"gated_mlp implements the 'silu' activation, not {activation!r}")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
-        self.names = dict(gate=prefix + gate_name, up=prefix + up_name, down=prefix + down_name)
+        self.names = dict(gate=prefix + gate_name, up=prefix + up_name, down=prefix + down_name,
+                          gate_b=prefix + gate_bias_name, up_b=prefix + up_bias_name, down_b=prefix + down_bias_name)
+        self.bias = bool(bias)
+        self.gate_up_bias: Optional[torch.Tensor] = None
+        self.down_bias: Optional[torch.Tensor] = None
         self.gate_up_weight: Optional[torch.Tensor] = None
         self.down_weight: Optional[torch.Tensor] = None
         self.paired = False
 
     def param_specs(self) -> list[ParamSpec]:
         h, i = self.hidden_size, self.intermediate_size
-        return [ParamSpec(self.names["gate"], (i, h)), ParamSpec(self.names["up"], (i, h)),
-                ParamSpec(self.names["down"], (h, i))]
+        specs = [ParamSpec(self.names["gate"], (i, h)), ParamSpec(self.names["up"], (i, h)),
+                 ParamSpec(self.names["down"], (h, i))]
+        if self.bias:
+            specs += [ParamSpec(self.names["gate_b"], (i,), "vector"), ParamSpec(self.names["up_b"], (i,), "vector"),
+                      ParamSpec(self.names["down_b"], (h,), "vector")]
+        return specs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         gate, up = tensors[self.names["gate"]], tensors[self.names["up"]]
-        self.paired = self.intermediate_size % kernels.GATE_UP_BLOCK == 0
+        self.paired = self.intermediate_size % kernels.GATE_UP_BLOCK == 0 and not self.bias
+        if self.bias:
+            self.gate_up_bias = torch.cat([tensors[self.names["gate_b"]].float(), tensors[self.names["up_b"]].float()]).contiguous()
+            self.down_bias = tensors[self.names["down_b"]].float().contiguous()
         if self.paired:
             self.gate_up_weight = kernels.interleave_gate_up(gate, up).contiguous()
         else:
@@ -76,5 +90,11 @@ class GatedMLP(Part):
         else:
             gate_up = ctx.buffer("gated_mlp.gate_up", (n, 2 * self.intermediate_size), x.dtype)
             kernels.linear(x, self.gate_up_weight, gate_up)
-            kernels.gated_linear(gate_up, self.down_weight, out)
+            if self.bias:
+                hidden = ctx.buffer("gated_mlp.hidden", (n, self.intermediate_size), x.dtype)
+                kernels.silu_mul(gate_up, hidden, bias=self.gate_up_bias)
+                kernels.linear(hidden, self.down_weight, out)
+                kernels.add_bias(out, self.down_bias)
+            else:
+                kernels.gated_linear(gate_up, self.down_weight, out)
         return out

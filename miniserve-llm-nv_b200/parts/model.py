@@ -83,9 +83,26 @@ class DecoderModel:
             if need is None:
                 runs.append(None)
                 continue
+            if isinstance(need, tuple):
+                # a mixer made of several (side by side): a cache of its own for every member that needs one
+                if run.cache_of is not None:
+                    raise ValueError(f"order[{index}]: a mixer of several members cannot read another run's cache")
+                plans = []
+                for member in need:
+                    if member is None:
+                        plans.append(None)
+                        continue
+                    if member not in keys:
+                        keys.append(member)
+                        counts.append(0)
+                    group = keys.index(member)
+                    plans.append(RunCache(group, counts[group], writable=True))
+                    counts[group] += 1
+                runs.append(tuple(plans))
+                continue
             if run.cache_of is not None:
                 source = runs[run.cache_of]
-                if source is None or self.cache_groups_need(keys, source.group) != need:
+                if source is None or isinstance(source, tuple) or self.cache_groups_need(keys, source.group) != need:
                     raise ValueError(f"order[{index}] cannot read the cache of entry {run.cache_of}: forms differ")
                 runs.append(RunCache(source.group, source.slot, writable=False))
                 continue

@@ -1,6 +1,8 @@
 """Norm parts.  ``rms``: ``weight * x * rsqrt(mean(x^2) + eps)`` with the statistics in float32
 (miniserve/model/layers.py:30-34), fused with the residual add that precedes it.  ``one_plus``: the stored weight
-lies around zero and stands for ``1 + weight`` (added once, in float32, when the weight is loaded)."""
+lies around zero and stands for ``1 + weight`` (added once, in float32, when the weight is loaded).  ``identity``: no norm
+at all, for blocks whose sublayers read the residual stream itself: what is pending is added and the stream is handed on in
+the compute type."""
 
 from __future__ import annotations
 
@@ -38,7 +40,8 @@ class RMSNorm(Part):
         """
         if isinstance(delta, PostNormed):
             # the output of the sublayer before passes its own norm on the way into the stream: one kernel for both
-            kernels.postnorm_add_rmsnorm(residual, delta.x, delta.weight, delta.eps, self.weight, self.eps, out, rows)
+            kernels.postnorm_add_rmsnorm(residual, delta.x, delta.weight, delta.eps, self.weight, self.eps, out, rows,
+                                         post_scale=delta.scale)
             return out
         second = None
         if isinstance(delta, tuple):
@@ -53,4 +56,24 @@ class RMSNorm(Part):
     def norm(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """Norm over the last dim of ``x`` (any leading shape) without a residual."""
         kernels.rmsnorm(x, self.weight, self.eps, out)
+        return out
+
+
+@register_norm("identity")
+class IdentityNorm(Part):
+    """The place of a norm in a block whose sublayers read the stream as it is (designs that norm a sublayer's output
+    only): ``add_and_norm`` adds what is pending into the float32 stream and writes the stream, rounded once to the compute
+    type, to ``out``.  It has no tensors."""
+
+    def __init__(self, *, size: int, prefix: str = "") -> None:
+        self.size = size
+
+    def add_and_norm(self, residual: torch.Tensor, delta, out: torch.Tensor,
+                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if delta is None:
+            kernels.postnorm_add_rmsnorm(residual, None, None, 0.0, None, 0.0, out, rows)
+        elif isinstance(delta, PostNormed):
+            kernels.postnorm_add_rmsnorm(residual, delta.x, delta.weight, delta.eps, None, 0.0, out, rows, post_scale=delta.scale)
+        else:
+            raise TypeError("the identity norm adds nothing, or an output that passes a norm of its own")
         return out

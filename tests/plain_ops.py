@@ -96,8 +96,10 @@ def qk_norm_rope_append(qkv, slots, q_weight, k_weight, eps, cos_sin, rotary_dim
         v_pool[page, :, offset, :] = v[token].to(v_pool.dtype)
 
 
-def silu_mul(gate_up, out, paired=False):
+def silu_mul(gate_up, out, paired=False, bias=None):
     n, inter = out.shape
+    if bias is not None:
+        gate_up = gate_up.double() + bias.double()
     if paired:      # blocks of sixteen columns: eight of the gate, then the same eight of the up projection
         blocks = gate_up.reshape(n, inter // 8, 2, 8)
         g, u = blocks[:, :, 0].reshape(n, inter).double(), blocks[:, :, 1].reshape(n, inter).double()
@@ -261,10 +263,10 @@ def router_topk(x, weight, bias, top, ids, weights, scratch=None, *, choose_from
         logits = logits + bias.double()
     if scratch is not None:
         scratch.copy_(logits.to(scratch.dtype))
-    if scoring == "all_softmax":
+    if scoring in ("all_softmax", "sigmoid"):
         total = logits.shape[1] if choose_from is None else choose_from
         n = logits.shape[0]
-        scores = torch.softmax(logits[:, :total], dim=1)
+        scores = torch.softmax(logits[:, :total], dim=1) if scoring == "all_softmax" else torch.sigmoid(logits[:, :total])
         choice = scores if correction is None else scores + correction.double()
         count, keep = groups
         if keep < count:
@@ -301,7 +303,7 @@ def clamped_glu(both, limit, out):
     out.copy_(clamped_glu_values(both[:, 0::2], both[:, 1::2], limit).to(out.dtype))
 
 
-def expert_linear(x, order, top, weight, out, offsets, relu_square=False, activation="none", limit=0.0):
+def expert_linear(x, order, top, weight, out, offsets, relu_square=False, activation="none", limit=0.0, pair_scale=None):
     for e in range(weight.shape[0]):
         lo, hi = int(offsets[e]), int(offsets[e + 1])
         if hi == lo:
@@ -312,11 +314,18 @@ def expert_linear(x, order, top, weight, out, offsets, relu_square=False, activa
             y = y.clamp(min=0).pow(2)
         elif activation == "clamped_glu":
             y = clamped_glu_values(y[:, 0::2], y[:, 1::2], limit)
+        elif activation == "silu_glu":
+            if pair_scale is not None:
+                y = y * pair_scale.double().reshape(-1)[order[lo:hi].long()][:, None]
+            y = y[:, 0::2] * torch.sigmoid(y[:, 0::2]) * y[:, 1::2]
         out[lo:hi] = y.to(out.dtype)
 
 
 def expert_combine(y, place, weights, shared, out, ids=None, first_identity=0, x=None, shared_gate=None, shared_gate_col=0):
-    n, top = weights.shape
+    n = out.shape[0]
+    top = place.numel() // max(n, 1) if weights is None else weights.shape[1]
+    if weights is None:
+        weights = torch.ones(n, top, dtype=torch.float64)
     picked = y.double()[place.long()].view(n, top, -1)
     if ids is not None:
         identity = (ids.long() >= first_identity)[:, :, None]
@@ -337,19 +346,24 @@ def relu_square(x):
 # --------------------------------------------------------------------------- norms on both sides, free projection layouts
 
 
-def postnorm_add_rmsnorm(residual, delta, post_weight, post_eps, weight, eps, out, rows=None):
-    d = delta.double()
-    add = post_weight.double() * (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps))
+def postnorm_add_rmsnorm(residual, delta, post_weight, post_eps, weight, eps, out, rows=None, post_scale=1.0):
+    add = 0.0
+    if delta is not None:
+        d = delta.double()
+        add = post_scale * post_weight.double() * (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps))
     if rows is None:
-        residual += add.to(residual.dtype)
+        if delta is not None:
+            residual += add.to(residual.dtype)
         x = residual.double()
     else:
         x = (residual.double() + add)[rows.long()]
-    out.copy_((weight.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))).to(out.dtype))
+    if weight is not None:
+        x = weight.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))
+    out.copy_(x.to(out.dtype))
 
 
 def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots, q_weight, k_weight, eps, cos_sin,
-                rotary_dim, k_pool, v_pool, q_out):
+                rotary_dim, k_pool, v_pool, q_out, interleaved=False):
     n = proj.shape[0]
 
     def heads(col, count, size, weight):
@@ -357,7 +371,7 @@ def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots
         if weight is not None:
             x = weight.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))
         if cos_sin is not None:
-            x = rotate(x, cos_sin, rotary_dim, False)
+            x = rotate(x, cos_sin, rotary_dim, interleaved)
         return x
 
     q_out.copy_(heads(q_col, n_q, head_dim, q_weight).to(q_out.dtype))
@@ -378,6 +392,11 @@ def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots
 
 
 def causal_conv_silu(proj, col, weight, bias, states, state_offset, state_slots, query_start, max_query_len, out):
+    causal_conv(proj, col, weight, bias, states, state_offset, state_slots, query_start, max_query_len, out)
+
+
+def causal_conv(proj, col, weight, bias, states, state_offset, state_slots, query_start, max_query_len, out, activation="silu",
+                in_bias=None):
     channels, taps = weight.shape
     keep = taps - 1
     for r in range(state_slots.numel()):
@@ -385,11 +404,14 @@ def causal_conv_silu(proj, col, weight, bias, states, state_offset, state_slots,
         if hi == lo:
             continue
         state = states[int(state_slots[r]), state_offset:state_offset + keep * channels].view(keep, channels)
-        u = torch.cat([state.double(), proj[lo:hi, col:col + channels].double()], dim=0)      # inputs -keep .. hi - lo - 1
-        total = bias.double().expand(hi - lo, -1).clone()
+        fresh = proj[lo:hi, col:col + channels].double()
+        if in_bias is not None:
+            fresh = fresh + in_bias.double()
+        u = torch.cat([state.double(), fresh], dim=0)      # inputs -keep .. hi - lo - 1
+        total = torch.zeros(hi - lo, channels, dtype=torch.float64) if bias is None else bias.double().expand(hi - lo, -1).clone()
         for k in range(taps):
             total = total + u[k:k + hi - lo] * weight[:, k].double()
-        out[lo:hi] = (total * torch.sigmoid(total)).to(out.dtype)
+        out[lo:hi] = (total * torch.sigmoid(total) if activation == "silu" else total).to(out.dtype)
         state.copy_(u[u.shape[0] - keep:].to(state.dtype))
 
 
@@ -419,6 +441,120 @@ def gated_group_norm(y, proj, z_col, weight, groups, eps, out):
     out.copy_((v * weight.double()).to(out.dtype))
 
 
+# --------------------------------------------------------------------------- recurrences that carry a matrix or a vector
+
+
+def add_bias(x, bias):
+    x.copy_((x.double() + bias.double()).to(x.dtype))
+
+
+def scaled_sum(a, a_scale, b, b_scale, out):
+    out.copy_((a_scale * a.double() + b_scale * b.double()).to(out.dtype))
+
+
+def small_linear_f32(x, weight, bias, out):
+    y = x.double() @ weight.double().T
+    out.copy_((y if bias is None else y + bias.double()).to(out.dtype))
+
+
+def unit_norm_heads(x, col, heads, dim, eps, scale):
+    v = x[:, col:col + heads * dim].double().view(-1, heads, dim)
+    v = scale * v / torch.sqrt(v.pow(2).sum(-1, keepdim=True) + eps)
+    x[:, col:col + heads * dim] = v.reshape(-1, heads * dim).to(x.dtype)
+
+
+def exponential_gates(logits, cap, states, state_offset, state_slots, query_start, max_query_len, gates):
+    heads = gates.shape[1]
+    squashed = cap * torch.tanh(logits.double() / cap)
+    log_i, log_f = squashed[:, :heads], torch.nn.functional.logsigmoid(squashed[:, heads:])
+    for r in range(state_slots.numel()):
+        lo, hi = int(query_start[r]), int(query_start[r + 1])
+        kept = states[int(state_slots[r]), state_offset:state_offset + heads]
+        peak = kept.double()
+        for t in range(lo, hi):
+            new_peak = torch.maximum(log_f[t] + peak, log_i[t])
+            gates[t, :, 0] = torch.exp(log_f[t] + peak - new_peak).to(gates.dtype)
+            gates[t, :, 1] = torch.exp(log_i[t] - new_peak).to(gates.dtype)
+            gates[t, :, 2] = torch.exp(-new_peak).to(gates.dtype)
+            peak = new_peak
+        if hi > lo:
+            kept.copy_(peak.to(kept.dtype))
+
+
+def decay_gates(logits, a_log, dt_bias, gates):
+    heads = gates.shape[1]
+    step = torch.nn.functional.softplus(logits[:, heads:].double() + dt_bias.double(), threshold=50.0)
+    gates[:, :, 0] = torch.exp(-torch.exp(a_log.double()) * step).to(gates.dtype)
+    gates[:, :, 1] = torch.sigmoid(logits[:, :heads].double()).to(gates.dtype)
+
+
+def matrix_scan(mode, q, q_col, k, k_col, v, v_col, gates, states, state_offset, state_slots, query_start, max_query_len, heads,
+                kv_heads, dim, vdim, y, q_scale=1.0, bottom=None):
+    per = heads // kv_heads
+    columns = vdim + 1 if mode == "memory" else vdim
+    for r in range(state_slots.numel()):
+        lo, hi = int(query_start[r]), int(query_start[r + 1])
+        if hi == lo:
+            continue
+        kept = states[int(state_slots[r]), state_offset:state_offset + heads * columns * dim].view(heads, columns, dim)
+        S = kept.double().clone()                # [head, column, dim]: column c of the matrix, the last one n
+        for t in range(lo, hi):
+            qt = (q_scale * q[t, q_col:q_col + kv_heads * dim].double()).view(kv_heads, dim).repeat_interleave(per, dim=0)
+            kt = k[t, k_col:k_col + kv_heads * dim].double().view(kv_heads, dim).repeat_interleave(per, dim=0)
+            vt = v[t, v_col:v_col + heads * vdim].double().view(heads, vdim)
+            g = gates[t].double()
+            if mode == "memory":
+                vt = torch.cat([vt, torch.ones(heads, 1, dtype=torch.float64)], dim=1)
+                S = g[:, 0, None, None] * S + g[:, 1, None, None] * vt[:, :, None] * kt[:, None, :]
+                read = torch.einsum("hcd,hd->hc", S, qt)
+                y[t] = read[:, :vdim].to(y.dtype)
+                bottom[t] = (torch.maximum(read[:, vdim].abs(), g[:, 2]) + 1e-6).to(bottom.dtype)
+            else:
+                S = g[:, 0, None, None] * S
+                u = g[:, 1, None] * (vt - torch.einsum("hcd,hd->hc", S, kt))
+                S = S + u[:, :, None] * kt[:, None, :]
+                y[t] = torch.einsum("hcd,hd->hc", S, qt).to(y.dtype)
+        kept.copy_(S.to(kept.dtype))
+
+
+def head_norm_gate(y, bottom, weight, gate, gate_col, activation, eps, out):
+    n, heads, vdim = y.shape
+    v = y.double()
+    if bottom is not None:
+        v = v / bottom.double()[:, :, None]
+    v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    w = weight.double().view(heads, vdim) if weight.numel() == heads * vdim else weight.double().view(1, vdim)
+    z = gate[:, gate_col:gate_col + heads * vdim].double().view(n, heads, vdim)
+    act = torch.sigmoid(z) if activation == "sigmoid" else z * torch.sigmoid(z)
+    out.copy_((v * w * act).reshape(n, heads * vdim).to(out.dtype))
+
+
+def gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+def gated_recurrence_scan(u, pre, gate_bias, rate, proj, y_col, y_bias, states, state_offset, state_slots, query_start,
+                          max_query_len, out):
+    width = u.shape[1]
+    r = torch.sigmoid(pre[0].double() + gate_bias[0].double())
+    i = torch.sigmoid(pre[1].double() + gate_bias[1].double())
+    log_a = rate.double() * r
+    a, b = torch.exp(log_a), torch.sqrt(-torch.expm1(2.0 * log_a))
+    z = proj[:, y_col:y_col + width].double()
+    if y_bias is not None:
+        z = z + y_bias.double()
+    for req in range(state_slots.numel()):
+        lo, hi = int(query_start[req]), int(query_start[req + 1])
+        if hi == lo:
+            continue
+        kept = states[int(state_slots[req]), state_offset:state_offset + width]
+        S = kept.double()
+        for t in range(lo, hi):
+            S = a[t] * S + b[t] * i[t] * u[t].double()
+            out[t] = (S * gelu_tanh(z[t])).to(out.dtype)
+        kept.copy_(S.to(kept.dtype))
+
+
 def install(monkeypatch) -> None:
     """Puts the functions above in place of the kernel bindings (CPU tests of host logic only)."""
     import miniserve_b200  # noqa: F401
@@ -428,7 +564,8 @@ def install(monkeypatch) -> None:
                  "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap", "latent_prepare",
                  "latent_attention", "head_gate", "linear_batched", "router_topk", "expert_route", "expert_linear",
                  "expert_combine", "relu_square", "clamped_glu", "postnorm_add_rmsnorm", "qkv_prepare", "causal_conv_silu",
-                 "selective_scan", "gated_group_norm"):
+                 "selective_scan", "gated_group_norm", "causal_conv", "add_bias", "scaled_sum", "small_linear_f32",
+                 "unit_norm_heads", "exponential_gates", "decay_gates", "matrix_scan", "head_norm_gate", "gated_recurrence_scan"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
     monkeypatch.setattr(kernels, "latent_attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
