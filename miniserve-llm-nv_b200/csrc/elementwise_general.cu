@@ -1,7 +1,9 @@
 // More memory-bound kernels between the matrix products, for blocks and mixers whose forms elementwise.cu does not cover:
 //
-//   ms_postnorm_add_rmsnorm   a sublayer's output is RMS-normed with a weight of its own, added to the float32 residual
-//                             stream, and the stream is RMS-normed for the next sublayer: one kernel, one pass over the row
+//   ms_postnorm_add_rmsnorm   a sublayer's output is RMS-normed with a weight of its own, added (times a constant) to the
+//                             float32 residual stream, and the stream is RMS-normed for the next sublayer, or handed on as
+//                             it is where the next sublayer reads the stream itself: one kernel, one pass over the row
+//   ms_silu_mul_bias, ms_add_bias, ms_scaled_sum   a gated activation and an output with biases; a weighted sum of two outputs
 //   ms_qkv_prepare            per-head norm, partial half-split rotation and paged append for a projection whose columns are
 //                             laid out freely: query heads of d numbers, key heads of d, value heads of dv (another size),
 //                             or queries alone (a layer that reads another layer's keys and values)
@@ -13,16 +15,16 @@
 namespace ms {
 
 // For output row k (source row r = rows ? rows[k] : k):
-//   a = post_weight * delta[r] / sqrt(mean(delta[r]^2) + post_eps)
+//   a = post_scale * post_weight * delta[r] / sqrt(mean(delta[r]^2) + post_eps)      (delta null: a = 0)
 //   x = residual[r] + a            (float32; written back to residual unless rows are gathered)
-//   out[k] = weight * x / sqrt(mean(x^2) + eps)     rounded once to T
+//   out[k] = weight * x / sqrt(mean(x^2) + eps)     rounded once to T      (weight null: out[k] = x)
 // The row (width <= blockDim.x * kPostNormPerThread) stays in registers between the passes.
 constexpr int kPostNormPerThread = 16;
 
 template <typename T>
 __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                             const void* __restrict__ post_weight, int post_weight_dtype, float post_eps,
-                                            const void* __restrict__ weight, int weight_dtype, float eps,
+                                            float post_scale, const void* __restrict__ weight, int weight_dtype, float eps,
                                             const int* __restrict__ rows, T* __restrict__ out, int hidden) {
   grid_dependency_wait();
   grid_dependency_launch();
@@ -36,26 +38,32 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ residual, const 
 #pragma unroll
   for (int i = 0; i < kPostNormPerThread; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
-    v[i] = c < hidden ? to_float(del[c]) : 0.f;
+    v[i] = (delta && c < hidden) ? to_float(del[c]) : 0.f;
     sum_sq += v[i] * v[i];
   }
-  const float inv_delta = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
+  float inv_delta = 0.f;
+  if (delta) inv_delta = post_scale / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
   sum_sq = 0.f;
 #pragma unroll
   for (int i = 0; i < kPostNormPerThread; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < hidden) {
-      v[i] = res[c] + load_as_float(post_weight, post_weight_dtype, c) * (v[i] * inv_delta);
-      if (rows == nullptr) res[c] = v[i];
+      if (delta) {
+        v[i] = res[c] + load_as_float(post_weight, post_weight_dtype, c) * (v[i] * inv_delta);
+        if (rows == nullptr) res[c] = v[i];
+      } else {
+        v[i] = res[c];
+      }
       sum_sq += v[i] * v[i];
     }
   }
-  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+  float inv = 1.f;
+  if (weight) inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
   T* dst = out + k * hidden;
 #pragma unroll
   for (int i = 0; i < kPostNormPerThread; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
-    if (c < hidden) dst[c] = from_float<T>(load_as_float(weight, weight_dtype, c) * (v[i] * inv));
+    if (c < hidden) dst[c] = from_float<T>(weight ? load_as_float(weight, weight_dtype, c) * (v[i] * inv) : v[i]);
   }
 }
 
@@ -64,7 +72,7 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ residual, const 
 template <typename T, int CHUNKS>
 __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                                 const void* __restrict__ post_weight, int post_weight_dtype, float post_eps,
-                                                const void* __restrict__ weight, int weight_dtype, float eps,
+                                                float post_scale, const void* __restrict__ weight, int weight_dtype, float eps,
                                                 const int* __restrict__ rows, T* __restrict__ out, int hidden) {
   grid_dependency_wait();
   grid_dependency_launch();
@@ -79,37 +87,44 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, co
   for (int i = 0; i < CHUNKS; ++i) {
     const int c = (i * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
-      v[i] = load8(del + c);
+      if (delta) v[i] = load8(del + c);
       x[i] = load8(res + c);                               // (on its way while the first sum is formed)
+      if (delta) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sum_sq += v[i].v[e] * v[i].v[e];
+        for (int e = 0; e < 8; ++e) sum_sq += v[i].v[e] * v[i].v[e];
+      }
     }
   }
-  const float inv_delta = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
+  float inv_delta = 0.f;
+  if (delta) inv_delta = post_scale / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
   sum_sq = 0.f;
 #pragma unroll
   for (int i = 0; i < CHUNKS; ++i) {
     const int c = (i * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
-      const Vec8 w = load8_any(post_weight, post_weight_dtype, c);
+      if (delta) {
+        const Vec8 w = load8_any(post_weight, post_weight_dtype, c);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        x[i].v[e] += w.v[e] * (v[i].v[e] * inv_delta);
-        sum_sq += x[i].v[e] * x[i].v[e];
+        for (int e = 0; e < 8; ++e) x[i].v[e] += w.v[e] * (v[i].v[e] * inv_delta);
+        if (rows == nullptr) store8(res + c, x[i]);
       }
-      if (rows == nullptr) store8(res + c, x[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum_sq += x[i].v[e] * x[i].v[e];
     }
   }
-  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+  float inv = 1.f;
+  if (weight) inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
   T* dst = out + k * hidden;
 #pragma unroll
   for (int i = 0; i < CHUNKS; ++i) {
     const int c = (i * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
-      const Vec8 w = load8_any(weight, weight_dtype, c);
-      Vec8 y;
+      Vec8 y = x[i];
+      if (weight) {
+        const Vec8 w = load8_any(weight, weight_dtype, c);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y.v[e] = w.v[e] * (x[i].v[e] * inv);
+        for (int e = 0; e < 8; ++e) y.v[e] = w.v[e] * (x[i].v[e] * inv);
+      }
       store8(dst + c, y);
     }
   }
@@ -120,14 +135,15 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, co
 //   q heads: optional RMS norm over d (weight float32), rotation, written to q_out[n, h, :]
 //   k heads: the same with their own weight, written to the key pool [page, kv_head, page_size, d] at the token's slot
 //   v heads: copied to the value pool [page, kv_head, page_size, dv]
-// Rotation: the first rotary_dim entries of a head, entry i paired with entry i + rotary_dim / 2; the pair (u, v)
+// Rotation: the first rotary_dim entries of a head, entry i paired with entry i + rotary_dim / 2 (interleaved: entry 2i with
+// entry 2i + 1); the pair (u, v)
 // becomes (u cos - v sin, v cos + u sin) with (cos, sin) = cos_sin[n, i].  A negative slot skips the writes.
 template <typename T>
 __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv,
                                    int d, int dv, const int* __restrict__ slots, const float* __restrict__ q_weight,
                                    const float* __restrict__ k_weight, float eps, const float2* __restrict__ cos_sin,
                                    int rotary_dim, T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
-                                   T* __restrict__ q_out, int n_tokens) {
+                                   T* __restrict__ q_out, int n_tokens, int interleaved) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float prepare_smem[];
@@ -178,12 +194,14 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col
     float v = x[c] * inv;
     if (weight) v *= weight[c];
     if (table && c < rotary_dim) {
-      const int j = c < half ? c : c - half;
-      const int partner = c < half ? c + half : c - half;
+      // the pair's first entry is c (partner behind it) or its second; half-split: (j, j + half), interleaved: (2j, 2j + 1)
+      const bool first = interleaved ? (c & 1) == 0 : c < half;
+      const int j = interleaved ? c >> 1 : (c < half ? c : c - half);
+      const int partner = interleaved ? c ^ 1 : (c < half ? c + half : c - half);
       float other = x[partner] * inv;
       if (weight) other *= weight[partner];
       const float2 cs = table[j];
-      v = c < half ? v * cs.x - other * cs.y : v * cs.x + other * cs.y;
+      v = first ? v * cs.x - other * cs.y : v * cs.x + other * cs.y;
     }
     dst[c] = from_float<T>(v);
   }
@@ -200,9 +218,11 @@ using namespace ms;
 
 // residual float32 [rows, hidden]; delta [rows, hidden] and out [n_out, hidden] of type `dtype`; the two weights [hidden]
 // in their own types; rows int32 [n_out] or null (then n_out rows in place, and the residual receives the sum).
+// delta null: nothing is added (post_weight is not read); weight null: out is the stream itself, rounded once.
 MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dtype, const void* post_weight,
-                                      int post_weight_dtype, float post_eps, const void* weight, int weight_dtype, float eps,
-                                      const int* rows, void* out, int n_out, int hidden, cudaStream_t stream) {
+                                      int post_weight_dtype, float post_eps, float post_scale, const void* weight,
+                                      int weight_dtype, float eps, const int* rows, void* out, int n_out, int hidden,
+                                      cudaStream_t stream) {
   if (n_out == 0) return 0;
   MS_REQUIRE(hidden > 0 && hidden <= 1024 * kPostNormPerThread, "postnorm_add_rmsnorm: width %d outside 1..%d", hidden,
              1024 * kPostNormPerThread);
@@ -212,7 +232,8 @@ MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dt
     const int chunks = (groups + vec_threads - 1) / vec_threads;
 #define MS_POSTNORM_VEC(C)                                                                                                   \
   MS_EG_DISPATCH(dtype, (ms::launch(postnorm_add_rmsnorm_vec_kernel<T, C>, n_out, vec_threads, 0, stream, residual,          \
-                                    (const T*)delta, post_weight, post_weight_dtype, post_eps, weight, weight_dtype, eps,   \
+                                    (const T*)delta, post_weight, post_weight_dtype, post_eps, post_scale, weight,           \
+                                    weight_dtype, eps,                                                                       \
                                     rows, (T*)out, hidden)))
     if (chunks == 1) { MS_POSTNORM_VEC(1); } else if (chunks == 2) { MS_POSTNORM_VEC(2); } else { MS_POSTNORM_VEC(4); }
 #undef MS_POSTNORM_VEC
@@ -223,7 +244,8 @@ MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dt
   if (threads < 128 && hidden >= 128) threads = 128;
   if (hidden >= 2048 && threads < 256) threads = 256;
   MS_EG_DISPATCH(dtype, (ms::launch(postnorm_add_rmsnorm_kernel<T>, n_out, threads, 0, stream, residual, (const T*)delta,
-                                    post_weight, post_weight_dtype, post_eps, weight, weight_dtype, eps, rows, (T*)out, hidden)));
+                                    post_weight, post_weight_dtype, post_eps, post_scale, weight, weight_dtype, eps, rows, (T*)out,
+                                    hidden)));
   MS_CHECK_LAUNCH("postnorm_add_rmsnorm");
   return 0;
 }
@@ -231,7 +253,7 @@ MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dt
 MS_EXPORT int ms_qkv_prepare(const void* proj, int dtype, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv, int d,
                              int dv, const int* slots, const float* q_weight, const float* k_weight, float eps,
                              const float* cos_sin, int rotary_dim, void* k_pool, void* v_pool, int page_size, void* q_out,
-                             int n_tokens, cudaStream_t stream) {
+                             int n_tokens, int interleaved, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(d > 0 && d <= 1024 && dv > 0, "qkv_prepare: head sizes %d and %d", d, dv);
   MS_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
@@ -245,7 +267,81 @@ MS_EXPORT int ms_qkv_prepare(const void* proj, int dtype, int ld, int q_col, int
   const size_t smem = (size_t)warps * d * sizeof(float);
   MS_EG_DISPATCH(dtype, (ms::launch(qkv_prepare_kernel<T>, (unsigned)blocks, warps * 32, smem, stream, (const T*)proj, ld, q_col,
                                     k_col, v_col, n_q, n_kv, d, dv, slots, q_weight, k_weight, eps, (const float2*)cos_sin,
-                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens)));
+                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens, interleaved)));
   MS_CHECK_LAUNCH("qkv_prepare");
+  return 0;
+}
+
+namespace ms {
+
+// out[n, c] = silu(gate_up[n, c] + bias[c]) * (gate_up[n, I + c] + bias[I + c])
+template <typename T>
+__global__ void silu_mul_bias_kernel(const T* __restrict__ gate_up, const float* __restrict__ bias, T* __restrict__ out,
+                                     size_t total, int inter) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t n = i / inter;
+  const int c = (int)(i % inter);
+  const float g = to_float(gate_up[n * 2 * inter + c]) + bias[c];
+  const float u = to_float(gate_up[n * 2 * inter + inter + c]) + bias[inter + c];
+  out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
+}
+
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, size_t total, int width) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  x[i] = from_float<T>(to_float(x[i]) + bias[i % width]);
+}
+
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ a, float a_scale, const T* __restrict__ b, float b_scale,
+                                  T* __restrict__ out, size_t total) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  out[i] = from_float<T>(a_scale * to_float(a[i]) + b_scale * to_float(b[i]));
+}
+
+}  // namespace ms
+
+// gate_up [n_tokens, 2 inter] (gate columns, then up columns); bias float32 [2 inter]; out [n_tokens, inter].
+MS_EXPORT int ms_silu_mul_bias(const void* gate_up, int dtype, const float* bias, void* out, int n_tokens, int inter,
+                               cudaStream_t stream) {
+  const long long total = (long long)n_tokens * inter;
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "silu_mul_bias: %lld elements in one launch is too many", total);
+  MS_EG_DISPATCH(dtype, (ms::launch(silu_mul_bias_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)gate_up, bias, (T*)out,
+                                    (size_t)total, inter)));
+  MS_CHECK_LAUNCH("silu_mul_bias");
+  return 0;
+}
+
+// x [rows, width] in place; bias float32 [width].
+MS_EXPORT int ms_add_bias(void* x, int dtype, const float* bias, int rows, int width, cudaStream_t stream) {
+  const long long total = (long long)rows * width;
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "add_bias: %lld elements in one launch is too many", total);
+  MS_EG_DISPATCH(dtype, (ms::launch(add_bias_kernel<T>, (unsigned)blocks, 256, 0, stream, (T*)x, bias, (size_t)total, width)));
+  MS_CHECK_LAUNCH("add_bias");
+  return 0;
+}
+
+// out = a_scale * a + b_scale * b over `total` elements (out may be a or b).
+MS_EXPORT int ms_scaled_sum(const void* a, float a_scale, const void* b, float b_scale, void* out, int dtype, long long total,
+                            cudaStream_t stream) {
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "scaled_sum: %lld elements in one launch is too many", total);
+  MS_EG_DISPATCH(dtype, (ms::launch(scaled_sum_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)a, a_scale, (const T*)b,
+                                    b_scale, (T*)out, (size_t)total)));
+  MS_CHECK_LAUNCH("scaled_sum");
   return 0;
 }

@@ -150,7 +150,7 @@ __global__ void router_select_kernel(const float* __restrict__ all_logits, int e
 // score that is not a number counts as the smallest, so that every id written is a valid one.
 __global__ void router_choose_kernel(const float* __restrict__ all_logits, int ld, int total, int top,
                                      const float* __restrict__ correction, int group_count, int group_keep,
-                                     int* __restrict__ ids, float* __restrict__ weights, int n_tokens) {
+                                     int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int sigmoid_scores) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float select_smem[];
@@ -173,7 +173,8 @@ __global__ void router_choose_kernel(const float* __restrict__ all_logits, int l
   sum = warp_sum(sum);
   __syncwarp();
   for (int e = lane; e < total; e += 32) {
-    const float v = score[e] / sum;
+    // scores: the softmax over all outputs, or the sigmoid of every output on its own
+    const float v = sigmoid_scores ? 1.f / (1.f + expf(-logits[e])) : score[e] / sum;
     score[e] = v;
     float c = v + (correction ? correction[e] : 0.f);
     if (!(c == c)) c = -3.0e38f;
@@ -253,7 +254,13 @@ __global__ void expert_route_kernel(const int* __restrict__ ids, int pairs, int 
 constexpr int EBM = 64, EBN = 64, EBK = 16, ETM = 4, ETN = 4;
 
 // epilogues of the experts' products
-enum : int { kActNone = 0, kActReluSquare = 1, kActClampedGlu = 2 };
+enum : int { kActNone = 0, kActReluSquare = 1, kActClampedGlu = 2, kActSiluGlu = 3 };
+
+// silu(s gate) (s up): the gated expert computed on s times its input (its first products are linear)
+__device__ __forceinline__ float silu_glu(float gate, float up, float s) {
+  const float g = s * gate;
+  return g / (1.f + expf(-g)) * (s * up);
+}
 
 // g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(1.702 g) (u + 1)
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit) {
@@ -268,7 +275,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 expert_linear_kernel(const T* __restrict__ A, int lda, const int* __restrict__ order, int top, const T* __restrict__ W,
                      T* __restrict__ C, int ldc, const int* __restrict__ offsets, int experts, int N, int K, int activation,
-                     float limit) {
+                     float limit, const float* __restrict__ pair_scale) {
   grid_dependency_wait();
   grid_dependency_launch();
   __shared__ float As[EBK][EBM + 4];
@@ -322,11 +329,14 @@ expert_linear_kernel(const T* __restrict__ A, int lda, const int* __restrict__ o
   for (int i = 0; i < ETM; ++i) {
     const int m = m0 + ty * ETM + i;
     if (m >= end) continue;
-    if (activation == kActClampedGlu) {           // columns alternate (gate, up): two of them give one result
+    if (activation >= kActClampedGlu) {           // columns alternate (gate, up): two of them give one result
+      const float s = (activation == kActSiluGlu && pair_scale) ? pair_scale[order[m]] : 1.f;
 #pragma unroll
       for (int j = 0; j < ETN; j += 2) {
         const int n = n0 + tx * ETN + j;
-        if (n + 1 < N) C[(size_t)m * ldc + n / 2] = from_float<T>(clamped_glu(acc[i][j], acc[i][j + 1], limit));
+        if (n + 1 < N)
+          C[(size_t)m * ldc + n / 2] = from_float<T>(activation == kActSiluGlu ? silu_glu(acc[i][j], acc[i][j + 1], s)
+                                                                                  : clamped_glu(acc[i][j], acc[i][j + 1], limit));
       }
       continue;
     }
@@ -355,7 +365,8 @@ template <int GBM, int GSTAGES>
 __global__ void __launch_bounds__(256)
 expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ order, int top,
                          const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ C, int ldc,
-                         const int* __restrict__ offsets, int experts, int N, int K, int activation, float limit) {
+                         const int* __restrict__ offsets, int experts, int N, int K, int activation, float limit,
+                         const float* __restrict__ pair_scale) {
   grid_dependency_wait();
   grid_dependency_launch();
   constexpr int GLD = GBK + 8;          // elements between the rows of a stage
@@ -451,6 +462,10 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int
           C[(size_t)m * ldc + n / 2] = __float2bfloat16_rn(clamped_glu(v0, v1, limit));
           continue;
         }
+        if (activation == kActSiluGlu) {
+          C[(size_t)m * ldc + n / 2] = __float2bfloat16_rn(silu_glu(v0, v1, pair_scale ? pair_scale[order[m]] : 1.f));
+          continue;
+        }
         if (activation == kActReluSquare) {
           v0 = fmaxf(v0, 0.f);
           v1 = fmaxf(v1, 0.f);
@@ -479,7 +494,7 @@ __global__ void expert_combine_kernel(const T* __restrict__ Y, int ldy, const in
     for (int k = 0; k < top; ++k) {
       const bool identity = ids && ids[n * top + k] >= first_identity;
       const float v = identity ? to_float(x[n * width + c]) : to_float(Y[(size_t)place[n * top + k] * ldy + c]);
-      sum += weights[n * top + k] * v;
+      sum += weights ? weights[n * top + k] * v : v;       // (no weights: the experts' inputs carried them)
     }
     if (shared) sum += share * to_float(shared[n * width + c]);
     out[n * width + c] = from_float<T>(sum);
@@ -558,12 +573,12 @@ MS_EXPORT int ms_router_topk(const void* x, int dtype, const float* weight, cons
   return 0;
 }
 
-// The router whose scores are the softmax over all outputs.  weight float32 [rows, width] with rows >= total: the first
+// The router whose scores are the softmax over all outputs (sigmoid_scores: the sigmoid of each output).  weight float32 [rows, width] with rows >= total: the first
 // `total` rows are the router's outputs, further rows ride along (their logits are left in `logits` for the caller);
 // bias [rows] or null; correction float32 [total] or null; logits float32 [n_tokens, rows]; ids, weights [n_tokens, top].
 MS_EXPORT int ms_router_choose(const void* x, int dtype, const float* weight, const float* bias, int width, int rows,
                                int total, int top, const float* correction, int group_count, int group_keep, float* logits,
-                               int* ids, float* weights, int n_tokens, cudaStream_t stream) {
+                               int* ids, float* weights, int n_tokens, int sigmoid_scores, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(total > 0 && rows >= total, "router_choose: %d outputs in %d rows", total, rows);
   MS_REQUIRE(group_count > 0 && total % group_count == 0 && group_keep >= 1 && group_keep <= group_count,
@@ -575,9 +590,17 @@ MS_EXPORT int ms_router_choose(const void* x, int dtype, const float* weight, co
   const size_t smem = (size_t)warps * (2 * total + group_count) * sizeof(float);
   MS_REQUIRE(smem <= 48 * 1024, "router_choose: %d outputs need %zu bytes of shared memory", total, smem);
   ms::launch(router_choose_kernel, (n_tokens + warps - 1) / warps, warps * 32, smem, stream, (const float*)logits, rows, total, top,
-             correction, group_count, group_keep, ids, weights, n_tokens);
+             correction, group_count, group_keep, ids, weights, n_tokens, sigmoid_scores);
   MS_CHECK_LAUNCH("router_choose: selection");
   return 0;
+}
+
+// out[n, r] = x[n] . weight[r] + bias[r] in float32: the router's logits kernel for any float32 weight of few rows (the gate
+// logits of a recurrence).  x [n_tokens, width] of type `dtype`; weight float32 [rows, width]; bias float32 [rows] or null.
+MS_EXPORT int ms_small_linear_f32(const void* x, int dtype, const float* weight, const float* bias, int width, int rows,
+                                  float* out, int n_tokens, cudaStream_t stream) {
+  if (n_tokens == 0 || rows == 0) return 0;
+  return launch_router_logits(x, dtype, weight, bias, width, rows, out, n_tokens, stream);
 }
 
 // ids [pairs] (each in 0 .. experts - 1); offsets [experts + 1]; order, place [pairs].
@@ -590,17 +613,20 @@ MS_EXPORT int ms_expert_route(const int* ids, int pairs, int experts, int* offse
 }
 
 // A rows of K numbers (row stride lda); order null or [pairs]; W [experts, N, K]; C [pairs, ldc].  activation: 0 none,
-// 1 squared ReLU, 2 the clamped gated one (the rows of W alternate gate, up; C then has N / 2 columns).
+// 1 squared ReLU, 2 the clamped gated one (the rows of W alternate gate, up; C then has N / 2 columns), 3 the silu-gated one
+// (the same layout; pair_scale float32 [pairs] or null, indexed by order[i]: the factor on the expert's input).
 MS_EXPORT int ms_expert_linear(const void* A, int dtype, int lda, const int* order, int top, const void* W, void* C, int ldc,
                                const int* offsets, int experts, int pairs, int N, int K, int activation, float limit,
-                               cudaStream_t stream) {
+                               const float* pair_scale, cudaStream_t stream) {
   if (pairs == 0 || N == 0 || experts == 0) return 0;
   MS_REQUIRE(K > 0 && top > 0, "expert_linear: inner size %d and choices %d must be positive", K, top);
-  MS_REQUIRE(activation >= kActNone && activation <= kActClampedGlu && (activation != kActClampedGlu || N % 2 == 0),
+  MS_REQUIRE(activation >= kActNone && activation <= kActSiluGlu && (activation < kActClampedGlu || N % 2 == 0),
              "expert_linear: activation %d with %d columns", activation, N);
+  MS_REQUIRE(pair_scale == nullptr || (activation == kActSiluGlu && order != nullptr),
+             "expert_linear: a scale per pair goes with the silu-gated activation and gathered rows");
   const int row_tiles = (pairs + EBM - 1) / EBM + experts;      // every segment may end in a partial tile
   MS_REQUIRE(row_tiles <= 65535, "expert_linear: %d rows in one launch is too many", pairs);
-  if (dtype == MS_BF16 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && (ldc % 2 == 0 || activation == kActClampedGlu)) {
+  if (dtype == MS_BF16 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && (ldc % 2 == 0 || activation >= kActClampedGlu)) {
     // long segments (256 rows an expert on average, or more): tiles of 128 rows; else tiles of 64
     const bool tall = pairs >= 256 * experts;
     const int rows = tall ? 128 : 64, stages = tall ? 3 : 4;
@@ -614,13 +640,13 @@ MS_EXPORT int ms_expert_linear(const void* A, int dtype, int lda, const int* ord
       allowed[tall] = true;
     }
     ms::launch(kernel, mma_grid, 256, smem, stream, (const __nv_bfloat16*)A, lda, order, top,
-               (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, offsets, experts, N, K, activation, limit);
+               (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, offsets, experts, N, K, activation, limit, pair_scale);
     MS_CHECK_LAUNCH("expert_linear (tensor cores)");
     return 0;
   }
   dim3 grid((N + EBN - 1) / EBN, row_tiles);
   MS_EXP_DISPATCH(dtype, (ms::launch(expert_linear_kernel<T>, grid, 256, 0, stream, (const T*)A, lda, order, top, (const T*)W,
-                                     (T*)C, ldc, offsets, experts, N, K, activation, limit)));
+                                     (T*)C, ldc, offsets, experts, N, K, activation, limit, pair_scale)));
   MS_CHECK_LAUNCH("expert_linear");
   return 0;
 }

@@ -1,0 +1,391 @@
+// Recurrent mixers that carry a matrix per head or a vector per layer from token to token: what lies between their input
+// projections and their output projection.
+//
+//   ms_unit_norm_heads        every head's vector becomes scale * v / sqrt(sum v^2 + eps), in place
+//   ms_exponential_gates      log gates with a soft cap, a running maximum carried by the request, and the three factors
+//                             (keep, write, floor) that a matrix memory with exponential gating needs per token and head
+//   ms_decay_gates            decay exp(-exp(A_log) softplus(a + dt_bias)) and write strength sigmoid(b) per token and head
+//   ms_matrix_scan            the recurrence over a dim x vdim matrix per head, in two forms:
+//                               memory: S = keep S + write k v^T, n = keep n + write k, y = S^T q, bottom = max(|n.q|, floor) + 1e-6
+//                               delta:  S = decay S, u = beta (v - S^T k), S = S + k u^T, y = S^T q
+//   ms_head_norm_gate         y / bottom, divided by its root mean square per head, times a weight, times sigmoid or SiLU of a gate
+//   ms_gated_recurrence_scan  S = a S + sqrt(1 - a^2) i u per channel with a = exp(rate sigmoid(.)), times gelu_tanh of a branch
+//
+// Everything here is float32 arithmetic on float32 state; only the projections that the kernels read and the last kernels'
+// outputs are in the model's compute type.  A request's tokens are walked in order and every sum has a fixed order, so a
+// position's result depends on the tokens before it alone, not on how they were cut into steps, on what else is in the
+// batch or on which state slot the request holds.
+#include "common.cuh"
+
+namespace ms {
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float log_sigmoid_f(float v) { return fminf(v, 0.f) - log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// One warp per (token, head) of x[n, ld]: the head's dim entries from column col + head dim.
+__global__ void unit_norm_heads_kernel(float* __restrict__ x, int ld, int col, int heads, int dim, float eps, float scale,
+                                       int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  float* v = x + (size_t)(item / heads) * ld + col + (size_t)(item % heads) * dim;
+  float sum_sq = 0.f;
+  for (int c = lane; c < dim; c += 32) sum_sq += v[c] * v[c];
+  const float factor = scale / sqrtf(warp_sum(sum_sq) + eps);
+  for (int c = lane; c < dim; c += 32) v[c] *= factor;
+}
+
+// One warp per (request, head).  logits [tokens, 2 heads] = [input | forget].  Lane l squashes the logits of token l of a
+// chunk of 32; the running maximum then walks the chunk's tokens in order (values handed round by shuffles), and each lane
+// writes its token's three factors.  The request's maximum is read from and left in states[slot, offset + head].
+__global__ void exponential_gates_kernel(const float* __restrict__ logits, float cap, float* __restrict__ states,
+                                         long long state_stride, int state_offset, const int* __restrict__ state_slots,
+                                         const int* __restrict__ query_start, int heads, float* __restrict__ gates) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x * warps + warp, request = blockIdx.y;
+  if (head >= heads) return;
+  const int q0 = query_start[request], q_len = query_start[request + 1] - q0;
+  if (q_len <= 0) return;
+  float* kept = states + (long long)state_slots[request] * state_stride + state_offset + head;
+  float peak = *kept;
+  for (int t0 = 0; t0 < q_len; t0 += 32) {
+    const int t = t0 + lane;
+    float log_i = 0.f, log_f = 0.f;
+    if (t < q_len) {
+      const float* row = logits + (size_t)(q0 + t) * 2 * heads;
+      log_i = cap * tanhf(row[head] / cap);
+      log_f = log_sigmoid_f(cap * tanhf(row[heads + head] / cap));
+    }
+    float before = 0.f, mine = 0.f;
+    const int count = min(32, q_len - t0);
+    for (int j = 0; j < count; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, log_f, j), ij = __shfl_sync(0xffffffffu, log_i, j);
+      const float next = fmaxf(fj + peak, ij);
+      if (lane == j) { before = peak; mine = next; }
+      peak = next;
+    }
+    if (t < q_len) {
+      float* out = gates + ((size_t)(q0 + t) * heads + head) * 3;
+      out[0] = expf(log_f + before - mine);
+      out[1] = expf(log_i - mine);
+      out[2] = expf(-mine);
+    }
+  }
+  if (lane == 0) *kept = peak;
+}
+
+// logits [tokens, 2 heads] = [b | a]; gates [tokens, heads, 2] = (decay, beta).
+__global__ void decay_gates_kernel(const float* __restrict__ logits, const float* __restrict__ a_log,
+                                   const float* __restrict__ dt_bias, float* __restrict__ gates, int n_tokens, int heads) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n_tokens * heads) return;
+  const int head = (int)(i % heads);
+  const float* row = logits + (size_t)(i / heads) * 2 * heads;
+  gates[2 * i] = expf(-expf(a_log[head]) * softplus_f(row[heads + head] + dt_bias[head]));
+  gates[2 * i + 1] = sigmoid_f(row[head]);
+}
+
+// The matrix recurrence.  grid (column tiles, heads, requests); a block of 128 threads owns 128 / LPC columns of one head's
+// matrix for one request, LPC lanes (a power of two) a column: lane `sub` holds the column's entries sub, sub + LPC, ... (R of
+// them, zero beyond dim) in registers.  In the memory form the matrix has one more column, n, whose "value" is 1 and whose
+// read-out n . q gives the token's divisor.  The tokens' keys, queries (times q_scale), values and gates pass through shared
+// memory in chunks of `tok` tokens; a column's sums are the lane's own entries in ascending order, then a butterfly over its
+// LPC lanes, whatever the chunk.
+constexpr int kScanThreads = 128;
+constexpr int kModeMemory = 0, kModeDelta = 1;
+
+template <typename T, int R, int MODE>
+__global__ void __launch_bounds__(kScanThreads)
+matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __restrict__ k, int k_ld, int k_col,
+                   const T* __restrict__ v, int v_ld, int v_col, float q_scale, const float* __restrict__ gates,
+                   float* __restrict__ states, long long state_stride, int state_offset,
+                   const int* __restrict__ state_slots, const int* __restrict__ query_start, int heads, int kv_heads, int dim,
+                   int vdim, int lpc_shift, int tok, float* __restrict__ y, float* __restrict__ bottom) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  extern __shared__ float matrix_smem[];
+  constexpr int G = MODE == kModeMemory ? 3 : 2;
+  const int LPC = 1 << lpc_shift, cols_per_block = kScanThreads >> lpc_shift;
+  const int dim_pad = LPC * R;
+  const int columns = MODE == kModeMemory ? vdim + 1 : vdim;
+  const int tid = threadIdx.x, cc = tid >> lpc_shift, sub = tid & (LPC - 1);
+  const int col = blockIdx.x * cols_per_block + cc;
+  const bool active = col < columns;
+  const int head = blockIdx.y, request = blockIdx.z;
+  const int kv_head = head / (heads / kv_heads);
+  const int q0 = query_start[request], q_len = query_start[request + 1] - q0;
+  if (q_len <= 0) return;                                    // (the whole block)
+  float* ks = matrix_smem;                                    // [tok][dim_pad]
+  float* qs = ks + tok * dim_pad;                             // [tok][dim_pad]
+  float* vs = qs + tok * dim_pad;                             // [tok][cols_per_block]
+  float* gs = vs + tok * cols_per_block;                      // [tok][4]
+  float* kept = states + (long long)state_slots[request] * state_stride + state_offset + ((size_t)head * columns + (active ? col : 0)) * dim;
+  float s[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = sub + LPC * r;
+    s[r] = (active && i < dim) ? kept[i] : 0.f;
+  }
+  for (int t0 = 0; t0 < q_len; t0 += tok) {
+    const int len = min(tok, q_len - t0);
+    __syncthreads();                                          // the chunk before has been read
+    for (int idx = tid; idx < len * dim_pad; idx += kScanThreads) {
+      const int tt = idx / dim_pad, i = idx - tt * dim_pad;
+      const size_t token = (size_t)(q0 + t0 + tt);
+      const bool real = i < dim;
+      ks[idx] = real ? to_float(k[token * k_ld + k_col + kv_head * dim + i]) : 0.f;
+      qs[idx] = real ? q_scale * to_float(q[token * q_ld + q_col + kv_head * dim + i]) : 0.f;
+    }
+    for (int idx = tid; idx < len * cols_per_block; idx += kScanThreads) {
+      const int tt = idx / cols_per_block, c = blockIdx.x * cols_per_block + (idx - tt * cols_per_block);
+      const size_t token = (size_t)(q0 + t0 + tt);
+      vs[idx] = c < vdim ? to_float(v[token * v_ld + v_col + head * vdim + c]) : 1.f;      // (the column n)
+    }
+    for (int idx = tid; idx < len * G; idx += kScanThreads) {
+      const int tt = idx / G, g = idx - tt * G;
+      gs[tt * 4 + g] = gates[((size_t)(q0 + t0 + tt) * heads + head) * G + g];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < len; ++tt) {
+      const float* kk = ks + tt * dim_pad + sub;
+      const float* qq = qs + tt * dim_pad + sub;
+      const float value = vs[tt * cols_per_block + cc];
+      const size_t token = (size_t)(q0 + t0 + tt);
+      float acc = 0.f;
+      if (MODE == kModeMemory) {
+        const float keep = gs[tt * 4], write = gs[tt * 4 + 1] * value;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          s[r] = keep * s[r] + write * kk[LPC * r];
+          acc += s[r] * qq[LPC * r];
+        }
+      } else {
+        const float decay = gs[tt * 4], beta = gs[tt * 4 + 1];
+        float seen = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          s[r] *= decay;
+          seen += s[r] * kk[LPC * r];
+        }
+        for (int o = LPC >> 1; o > 0; o >>= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
+        const float u = beta * (value - seen);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          s[r] += kk[LPC * r] * u;
+          acc += s[r] * qq[LPC * r];
+        }
+      }
+      for (int o = LPC >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0 && active) {
+        if (col < vdim) {
+          y[(token * heads + head) * vdim + col] = acc;
+        } else {
+          bottom[token * heads + head] = fmaxf(fabsf(acc), gs[tt * 4 + 2]) + 1e-6f;
+        }
+      }
+    }
+  }
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = sub + LPC * r;
+      if (i < dim) kept[i] = s[r];
+    }
+  }
+}
+
+// One warp per (token, head): v = y / bottom, v / sqrt(mean(v^2) + eps) * weight * act(gate).
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ bottom,
+                                      const float* __restrict__ weight, int weight_per_head, const T* __restrict__ gate,
+                                      int gate_ld, int gate_col, int activation, float eps, T* __restrict__ out, int n_tokens,
+                                      int heads, int vdim) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const size_t token = (size_t)(item / heads);
+  const int head = (int)(item % heads);
+  const float* row = y + (size_t)item * vdim;
+  const float divisor = bottom ? bottom[item] : 1.f;
+  float sum_sq = 0.f;
+  for (int c = lane; c < vdim; c += 32) {
+    const float value = row[c] / divisor;
+    sum_sq += value * value;
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)vdim + eps);
+  const float* w = weight + (weight_per_head ? (size_t)head * vdim : 0);
+  const T* z = gate + token * gate_ld + gate_col + (size_t)head * vdim;
+  T* dst = out + (token * heads + head) * vdim;
+  for (int c = lane; c < vdim; c += 32) {
+    const float g = to_float(z[c]);
+    const float factor = activation ? g * sigmoid_f(g) : sigmoid_f(g);
+    dst[c] = from_float<T>((row[c] / divisor) * inv * w[c] * factor);
+  }
+}
+
+// grid (channel blocks, requests); a thread owns one channel and walks the request's tokens with the state in a register.
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_recurrence_scan_kernel(const float* __restrict__ u, const float* __restrict__ pre, const float* __restrict__ gate_bias,
+                             const float* __restrict__ rate, const T* __restrict__ proj, int ld, int y_col,
+                             const float* __restrict__ y_bias, float* __restrict__ states, long long state_stride,
+                             int state_offset, const int* __restrict__ state_slots, const int* __restrict__ query_start,
+                             int width, int n_tokens, T* __restrict__ out) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, request = blockIdx.y;
+  const int q0 = query_start[request], q_len = query_start[request + 1] - q0;
+  if (c >= width || q_len <= 0) return;
+  float* kept = states + (long long)state_slots[request] * state_stride + state_offset + c;
+  const float r_bias = gate_bias[c], i_bias = gate_bias[width + c], slope = rate[c], branch_bias = y_bias ? y_bias[c] : 0.f;
+  const float* pre_r = pre + (size_t)q0 * width + c;
+  const float* pre_i = pre + ((size_t)n_tokens + q0) * width + c;
+  const float* input = u + (size_t)q0 * width + c;
+  const T* branch = proj + (size_t)q0 * ld + y_col + c;
+  T* dst = out + (size_t)q0 * width + c;
+  float state = *kept;
+#pragma unroll 4
+  for (int t = 0; t < q_len; ++t) {
+    const float r = sigmoid_f(pre_r[(size_t)t * width] + r_bias);
+    const float gate_in = sigmoid_f(pre_i[(size_t)t * width] + i_bias);
+    const float log_a = slope * r;
+    const float a = expf(log_a), spread = sqrtf(-expm1f(2.f * log_a));       // sqrt(1 - a^2) without cancellation
+    state = a * state + spread * (gate_in * input[(size_t)t * width]);
+    dst[(size_t)t * width] = from_float<T>(state * gelu_tanh_f(to_float(branch[(size_t)t * ld]) + branch_bias));
+  }
+  *kept = state;
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+#define MS_REC_DISPATCH(dtype, ...)                              \
+  if ((dtype) == MS_F32) { using T = float; __VA_ARGS__; }       \
+  else if ((dtype) == MS_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+  else MS_FAIL("unknown element type code %d", (dtype));
+
+// x float32 [n_tokens, ld], in place.
+MS_EXPORT int ms_unit_norm_heads(float* x, int ld, int col, int heads, int dim, float eps, float scale, int n_tokens,
+                                 cudaStream_t stream) {
+  if (n_tokens == 0 || heads == 0) return 0;
+  MS_REQUIRE(dim > 0 && col >= 0 && col + heads * dim <= ld, "unit_norm_heads: %d heads of %d from column %d of rows of %d", heads, dim, col, ld);
+  const int warps = 4;
+  const long long blocks = ((long long)n_tokens * heads + warps - 1) / warps;
+  MS_REQUIRE(blocks < 2147483647LL, "unit_norm_heads: %lld heads in one launch is too many", (long long)n_tokens * heads);
+  ms::launch(unit_norm_heads_kernel, (unsigned)blocks, warps * 32, 0, stream, x, ld, col, heads, dim, eps, scale, n_tokens);
+  MS_CHECK_LAUNCH("unit_norm_heads");
+  return 0;
+}
+
+// logits float32 [tokens, 2 heads]; states float32 rows of state_stride numbers, the heads' maxima at state_offset;
+// gates float32 [tokens, heads, 3].
+MS_EXPORT int ms_exponential_gates(const float* logits, float cap, float* states, long long state_stride, int state_offset,
+                                   const int* state_slots, const int* query_start, int n_requests, int heads, float* gates,
+                                   cudaStream_t stream) {
+  if (n_requests == 0 || heads == 0) return 0;
+  MS_REQUIRE(cap > 0.f && n_requests <= 65535, "exponential_gates: cap %f, %d requests", cap, n_requests);
+  const int warps = heads >= 4 ? 4 : heads;
+  dim3 grid((heads + warps - 1) / warps, n_requests);
+  ms::launch(exponential_gates_kernel, grid, warps * 32, 0, stream, logits, cap, states, state_stride, state_offset, state_slots,
+             query_start, heads, gates);
+  MS_CHECK_LAUNCH("exponential_gates");
+  return 0;
+}
+
+MS_EXPORT int ms_decay_gates(const float* logits, const float* a_log, const float* dt_bias, float* gates, int n_tokens,
+                             int heads, cudaStream_t stream) {
+  const long long total = (long long)n_tokens * heads;
+  if (total == 0) return 0;
+  ms::launch(decay_gates_kernel, (unsigned)((total + 127) / 128), 128, 0, stream, logits, a_log, dt_bias, gates, n_tokens, heads);
+  MS_CHECK_LAUNCH("decay_gates");
+  return 0;
+}
+
+// mode 0 (memory): gates [tokens, heads, 3], state [heads, vdim + 1, dim] per slot, bottom [tokens, heads];
+// mode 1 (delta): gates [tokens, heads, 2], state [heads, vdim, dim], bottom unused.  q, k, v: rows of q_ld, k_ld, v_ld
+// numbers of type `dtype`; y float32 [tokens, heads, vdim].  max_query_len: an upper bound of the tokens a request brings.
+MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const void* k, int k_ld, int k_col, const void* v,
+                             int v_ld, int v_col, int dtype, float q_scale, const float* gates, float* states,
+                             long long state_stride, int state_offset, const int* state_slots, const int* query_start,
+                             int n_requests, int max_query_len, int heads, int kv_heads, int dim, int vdim, float* y,
+                             float* bottom, cudaStream_t stream) {
+  if (n_requests == 0 || max_query_len <= 0 || heads == 0) return 0;
+  MS_REQUIRE(mode == kModeMemory || mode == kModeDelta, "matrix_scan: mode %d", mode);
+  MS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0 && dim >= 1 && dim <= 512 && vdim >= 1, "matrix_scan: %d/%d heads of %d/%d",
+             heads, kv_heads, dim, vdim);
+  MS_REQUIRE(mode != kModeMemory || bottom != nullptr, "matrix_scan: the memory form writes the tokens' divisors");
+  MS_REQUIRE(heads <= 65535 && n_requests <= 65535, "matrix_scan: grid %d x %d exceeds the launch limits", heads, n_requests);
+  // lanes per column: aim at eight entries a lane; sixteen where a warp would not hold the column otherwise
+  int lpc_shift = 0;
+  while (lpc_shift < 5 && (dim + (1 << lpc_shift) - 1) / (1 << lpc_shift) > 8) ++lpc_shift;
+  const int per_lane = (dim + (1 << lpc_shift) - 1) >> lpc_shift;
+  const int r = per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : 16;
+  const int cols_per_block = kScanThreads >> lpc_shift;
+  const int columns = mode == kModeMemory ? vdim + 1 : vdim;
+  const int row_floats = 2 * (r << lpc_shift) + cols_per_block + 4;
+  int tok = max_query_len < 16 ? max_query_len : 16;
+  while (tok > 1 && (size_t)tok * row_floats * sizeof(float) > 40 * 1024) tok >>= 1;
+  const size_t smem = (size_t)tok * row_floats * sizeof(float);
+  dim3 grid((columns + cols_per_block - 1) / cols_per_block, heads, n_requests);
+#define MS_MATRIX_SCAN(R, MODE)                                                                                               \
+  MS_REC_DISPATCH(dtype, (ms::launch(matrix_scan_kernel<T, R, MODE>, grid, kScanThreads, smem, stream, (const T*)q, q_ld, q_col, \
+                                     (const T*)k, k_ld, k_col, (const T*)v, v_ld, v_col, q_scale, gates, states, state_stride,  \
+                                     state_offset, state_slots, query_start, heads, kv_heads, dim, vdim, lpc_shift, tok, y,     \
+                                     bottom)))
+  if (mode == kModeMemory) {
+    if (r == 4) { MS_MATRIX_SCAN(4, kModeMemory); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeMemory); } else { MS_MATRIX_SCAN(16, kModeMemory); }
+  } else {
+    if (r == 4) { MS_MATRIX_SCAN(4, kModeDelta); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeDelta); } else { MS_MATRIX_SCAN(16, kModeDelta); }
+  }
+#undef MS_MATRIX_SCAN
+  MS_CHECK_LAUNCH("matrix_scan");
+  return 0;
+}
+
+// y float32 [tokens, heads, vdim]; bottom float32 [tokens, heads] or null; weight float32 [heads * vdim] (weight_per_head) or
+// [vdim]; gate rows of gate_ld numbers of type `dtype`; activation 0: sigmoid, 1: SiLU; out [tokens, heads * vdim].
+MS_EXPORT int ms_head_norm_gate(const float* y, const float* bottom, const float* weight, int weight_per_head, const void* gate,
+                                int dtype, int gate_ld, int gate_col, int activation, float eps, void* out, int n_tokens,
+                                int heads, int vdim, cudaStream_t stream) {
+  if (n_tokens == 0 || heads == 0 || vdim == 0) return 0;
+  MS_REQUIRE(activation == 0 || activation == 1, "head_norm_gate: activation code %d", activation);
+  const int warps = 4;
+  const long long blocks = ((long long)n_tokens * heads + warps - 1) / warps;
+  MS_REQUIRE(blocks < 2147483647LL, "head_norm_gate: %lld heads in one launch is too many", (long long)n_tokens * heads);
+  MS_REC_DISPATCH(dtype, (ms::launch(head_norm_gate_kernel<T>, (unsigned)blocks, warps * 32, 0, stream, y, bottom, weight,
+                                     weight_per_head, (const T*)gate, gate_ld, gate_col, activation, eps, (T*)out, n_tokens,
+                                     heads, vdim)));
+  MS_CHECK_LAUNCH("head_norm_gate");
+  return 0;
+}
+
+// u float32 [tokens, width]; pre float32 [2, tokens, width]; gate_bias float32 [2, width]; rate float32 [width]; proj rows of ld
+// numbers of type `dtype` (the gated branch at y_col); y_bias float32 [width] or null; the state [width] at state_offset of a
+// slot's row; out [tokens, width] of type `dtype`.
+MS_EXPORT int ms_gated_recurrence_scan(const float* u, const float* pre, const float* gate_bias, const float* rate,
+                                       const void* proj, int dtype, int ld, int y_col, const float* y_bias, float* states,
+                                       long long state_stride, int state_offset, const int* state_slots,
+                                       const int* query_start, int n_requests, int n_tokens, int width, void* out,
+                                       cudaStream_t stream) {
+  if (n_requests == 0 || n_tokens == 0 || width == 0) return 0;
+  MS_REQUIRE(n_requests <= 65535, "gated_recurrence_scan: %d requests exceed the launch limits", n_requests);
+  dim3 grid((width + 127) / 128, n_requests);
+  MS_REC_DISPATCH(dtype, (ms::launch(gated_recurrence_scan_kernel<T>, grid, 128, 0, stream, u, pre, gate_bias, rate, (const T*)proj,
+                                     ld, y_col, y_bias, states, state_stride, state_offset, state_slots, query_start, width,
+                                     n_tokens, (T*)out)));
+  MS_CHECK_LAUNCH("gated_recurrence_scan");
+  return 0;
+}

@@ -1,7 +1,7 @@
 // The selective state-space mixer: what lies between its input projection and its output projection.
 //
-//   ms_causal_conv_silu   per channel a causal convolution of a few taps with a bias, then SiLU, over the tokens of every
-//                         request in the batch; the request's last (taps - 1) inputs are kept in its state vector
+//   ms_causal_conv        per channel a causal convolution of a few taps with a bias, then SiLU (or nothing), over the tokens
+//                         of every request in the batch; the request's last (taps - 1) inputs are kept in its state vector
 //   ms_selective_scan     per head S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T and y_t = S_t^T C_t + D x_t with
 //                         dt_t = softplus(dt_t + dt_bias), walked token by token from the state the request's slot holds
 //   ms_gated_group_norm   out = weight * (y silu(z)) / rms(y silu(z)), the root mean square taken per group of channels
@@ -26,10 +26,13 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 // grid (channel blocks, token chunks, requests); a thread owns one channel and walks kConvTokens tokens with the last
 // inputs in registers.  The block of a request's FIRST chunk also writes the request's new convolution state: it is the
 // only block that reads the old one (into registers, before anything is written), so nothing races.
+// `in_bias` (or null) is added to every input read from `proj` (the bias of the projection that made it; the state keeps
+// inputs with it, and the zeros before a sequence's start stay zeros); `bias` (or null) is the convolution's own.
 template <typename T>
 __global__ void __launch_bounds__(128)
 causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channels, int taps,
-                        const float* __restrict__ weight, const float* __restrict__ bias, float* __restrict__ states,
+                        const float* __restrict__ weight, const float* __restrict__ bias,
+                        const float* __restrict__ in_bias, int activation, float* __restrict__ states,
                         long long state_stride, int state_offset, const int* __restrict__ state_slots,
                         const int* __restrict__ query_start, float* __restrict__ out) {
   grid_dependency_wait();
@@ -44,7 +47,8 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
   float w[kMaxTaps], window[kMaxTaps];       // window[k]: the input that tap k meets at the current token
 #pragma unroll
   for (int k = 0; k < kMaxTaps; ++k) w[k] = k < taps ? weight[(size_t)c * taps + k] : 0.f;
-  const float b = bias[c];
+  const float b = bias ? bias[c] : 0.f;
+  const float ib = in_bias ? in_bias[c] : 0.f;
   // inputs before token t0: from the batch where the request's portion reaches back that far, else from the state
   // (the input at local index i < 0 is state[keep + i])
 #pragma unroll
@@ -53,7 +57,7 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
   for (int k = 0; k + 1 < kMaxTaps; ++k) {
     if (k + 1 < taps) {                      // slots 1 .. taps - 1 hold inputs t0 - keep + k .. ; slot 0 is shifted out first
       const int i = t0 - keep + k;
-      window[k + 1] = i >= 0 ? to_float(proj[(size_t)(q0 + i) * ld + col + c]) : state[(size_t)(keep + i) * channels + c];
+      window[k + 1] = i >= 0 ? to_float(proj[(size_t)(q0 + i) * ld + col + c]) + ib : state[(size_t)(keep + i) * channels + c];
     }
   }
   if (t0 == 0) {
@@ -62,7 +66,7 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
       const int i = q_len - keep + j;        // local index of the input that becomes state[j]
       float v = 0.f;
       if (i >= 0) {
-        v = to_float(proj[(size_t)(q0 + i) * ld + col + c]);
+        v = to_float(proj[(size_t)(q0 + i) * ld + col + c]) + ib;
       } else {
 #pragma unroll
         for (int k = 1; k < kMaxTaps; ++k)
@@ -77,14 +81,14 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
 #pragma unroll
     for (int k = 0; k + 1 < kMaxTaps; ++k) window[k] = window[k + 1];
     // after the shift the newest input belongs at index taps - 1
-    const float u = to_float(proj[(size_t)(q0 + t) * ld + col + c]);
+    const float u = to_float(proj[(size_t)(q0 + t) * ld + col + c]) + ib;
     float sum = b;
 #pragma unroll
     for (int k = 0; k < kMaxTaps; ++k) {
       if (k == taps - 1) window[k] = u;
       if (k < taps) sum += w[k] * window[k];
     }
-    out[(size_t)(q0 + t) * channels + c] = silu_f(sum);
+    out[(size_t)(q0 + t) * channels + c] = activation ? silu_f(sum) : sum;
   }
 }
 
@@ -402,20 +406,23 @@ using namespace ms;
   else MS_FAIL("unknown element type code %d", (dtype));
 
 // proj [tokens, ld]: the convolution's inputs are its columns col .. col + channels; weight float32 [channels, taps] (the
-// last tap is the current token's), bias float32 [channels]; states float32, one row of state_stride numbers per slot,
-// the convolution's part at state_offset; out float32 [tokens, channels].
-MS_EXPORT int ms_causal_conv_silu(const void* proj, int dtype, int ld, int col, int channels, int taps, const float* weight,
-                                  const float* bias, float* states, long long state_stride, int state_offset,
-                                  const int* state_slots, const int* query_start, int n_requests, int max_query_len,
-                                  float* out, cudaStream_t stream) {
+// last tap is the current token's), bias float32 [channels] or null; in_bias float32 [channels] or null (added to the inputs
+// as they are read); activation 0: none, 1: SiLU; states float32, one row of state_stride numbers per slot, the
+// convolution's part at state_offset; out float32 [tokens, channels].
+MS_EXPORT int ms_causal_conv(const void* proj, int dtype, int ld, int col, int channels, int taps, const float* weight,
+                             const float* bias, const float* in_bias, int activation, float* states, long long state_stride,
+                             int state_offset, const int* state_slots, const int* query_start, int n_requests,
+                             int max_query_len, float* out, cudaStream_t stream) {
   if (n_requests == 0 || max_query_len == 0 || channels == 0) return 0;
-  MS_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal_conv_silu: %d taps outside 1..%d", taps, kMaxTaps);
+  MS_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal_conv: %d taps outside 1..%d", taps, kMaxTaps);
+  MS_REQUIRE(activation == 0 || activation == 1, "causal_conv: activation code %d", activation);
   const int chunks = (max_query_len + kConvTokens - 1) / kConvTokens;
-  MS_REQUIRE(chunks <= 65535 && n_requests <= 65535, "causal_conv_silu: grid %d x %d exceeds the launch limits", chunks, n_requests);
+  MS_REQUIRE(chunks <= 65535 && n_requests <= 65535, "causal_conv: grid %d x %d exceeds the launch limits", chunks, n_requests);
   dim3 grid((channels + 127) / 128, chunks, n_requests);
   MS_SS_DISPATCH(dtype, (ms::launch(causal_conv_silu_kernel<T>, grid, 128, 0, stream, (const T*)proj, ld, col, channels, taps,
-                                    weight, bias, states, state_stride, state_offset, state_slots, query_start, out)));
-  MS_CHECK_LAUNCH("causal_conv_silu");
+                                    weight, bias, in_bias, activation, states, state_stride, state_offset, state_slots,
+                                    query_start, out)));
+  MS_CHECK_LAUNCH("causal_conv");
   return 0;
 }
 

@@ -890,7 +890,7 @@ def gated_recurrence_scan(u: torch.Tensor, pre: torch.Tensor, gate_bias: torch.T
     stride = _state_rows(states, state_offset, width)
     _check(library().ms_gated_recurrence_scan(_ptr(u), _ptr(pre), _ptr(gate_bias), _ptr(rate), _ptr(proj), _i(_code(proj.dtype)),
                                               _i(proj.shape[1]), _i(y_col), _ptr(y_bias), _ptr(states), stride, _i(state_offset),
-                                              _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(max_query_len), _i(width),
+                                              _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(n), _i(width),
                                               _ptr(out), _stream()))
 
 
