@@ -501,6 +501,24 @@ def _zozezen(width, heads, kv_heads, head, ssm_heads, ssm_head, state, groups, e
     return dict(architecture="Zozezen", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=entries)
 
 
+def _kivurax(width, memory, delta, left, right, dense_ff, experts, top, expert_ff, vocab):
+    """Four layers: matrix memory with a gated feed-forward, delta rule with experts, windowed attention beside a gated linear
+    recurrence with experts, matrix memory with a gated feed-forward."""
+    moe = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top))
+    dense = dict(kind="dense", ff=dense_ff)
+    heads, dim, vdim = memory
+    mlstm = dict(type="mlstm", mixer=dict(heads=heads, dim=dim, vdim=vdim, gate_cap=15.0))
+    heads, kv_heads, dim, vdim = delta
+    rule = dict(type="delta", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=4))
+    heads, kv_heads, dim, window = left
+    attention = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, mask=dict(size=window),
+                     rot=dict(base=1000000.0, dims=dim // 2, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)))
+    channels, blocks = right
+    side = dict(type="parallel", mixer=dict(left=attention, right=dict(width=channels, blocks=blocks, conv=4), left_scale=1.0, right_scale=1.0))
+    entries = [dict(mlstm, mlp=dense), dict(rule, mlp=moe), dict(side, mlp=moe), dict(mlstm, mlp=dense)]
+    return dict(architecture="Kivurax", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, layers=entries)
+
+
 # Layer sizes that resemble real models' (random weights, four layers each: two with a gated MLP, two with experts), and
 # the Qwen3 layers of equal width, head count and inner size beside them.
 DESIGN_SIZES = {
@@ -517,11 +535,23 @@ DESIGN_SIZES = {
     # latent 512 + 64, sixteen heads of 128 + 64; 64 experts of 1,408, six per token, and a shared one of 2,816
     "lite": dict(vesidra=_vesidra(2048, 4, _latent(16, 128, 64, 128, 512), 10944, 64, 6, 1408, 2816, 32000),
                  qwen3=dict(hidden_size=2048, intermediate_size=10944, num_attention_heads=16, num_key_value_heads=8, head_dim=128)),
+    # Kivurax: a matrix memory of eight heads (keys of 128, values of 256), a delta rule of sixteen value heads of 128 over eight
+    # query/key heads, sixteen heads of 128 over four key heads under a window of 1,024 beside a recurrence of 2,048 channels in
+    # sixteen parts; 16 experts of 1,024, four per token; beside it Zozezen (the closest design: recurrent and attention layers,
+    # a sink, norms on the sublayers' outputs, experts) and Qwen3 at the same width
+    "recurrent-small": dict(kivurax=_kivurax(2048, (8, 128, 256), (16, 8, 128, 128), (16, 4, 128, 1024), (2048, 16), 6144, 16, 4, 1024, 32000),
+                            zozezen=_zozezen(2048, 16, 4, 128, 64, 64, 128, 8, 16, 0, 4, 1024, 2048, 32000),
+                            qwen3=dict(hidden_size=2048, intermediate_size=6144, num_attention_heads=16, num_key_value_heads=4, head_dim=128)),
+    # the same with heads of 64 everywhere, a window of 512, a recurrence of 2,560 channels in twenty parts, 60 experts of 1,408,
+    # six per token
+    "recurrent-lite": dict(kivurax=_kivurax(2048, (16, 64, 128), (32, 16, 64, 64), (32, 8, 64, 512), (2560, 20), 10944, 60, 6, 1408, 32000),
+                           zozezen=_zozezen(2048, 32, 8, 64, 32, 128, 64, 4, 60, 4, 6, 1408, 2816, 32000),
+                           qwen3=dict(hidden_size=2048, intermediate_size=10944, num_attention_heads=32, num_key_value_heads=8, head_dim=64)),
 }
 
 
 def designs_workload(args) -> int:
-    """``--workload designs``: prompt and decode throughput of Vesidra and of Zozezen at sizes that resemble real models' layers, beside
+    """``--workload designs``: prompt and decode throughput of Vesidra, Zozezen and Kivurax at sizes that resemble real models' layers, beside
     the Qwen3 decoder at equal width, depth, head count and inner size; one JSON line per size and design, with each
     step's kernels (device time by kernel, from the framework profiler) so that like kernels can be set side by side."""
     import torch
@@ -672,7 +702,7 @@ def main() -> int:
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--workload", choices=("default", "mixed", "sweep", "designs"), default="default",
-                        help="designs: Vesidra and Zozezen beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
+                        help="designs: Vesidra, Zozezen and Kivurax beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="with --workload designs: one size only")
     parser.add_argument("--sweep-prompt", type=int, default=1024)
     parser.add_argument("--sweep-new", type=int, default=128)
