@@ -46,6 +46,7 @@ def build_qwen3_spec(config: Qwen3Config) -> ModelSpec:
         max_positions=config.max_position_embeddings,
         # Qwen3 snapshots store lm_head.weight even when it is tied to the embedding.
         optional_names=("lm_head.weight",) if config.tie_word_embeddings else (),
+        tied_copies=("lm_head.weight",) if config.tie_word_embeddings else (),
     )
 
 

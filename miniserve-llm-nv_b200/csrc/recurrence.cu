@@ -96,13 +96,20 @@ __global__ void decay_gates_kernel(const float* __restrict__ logits, const float
 }
 
 // The matrix recurrence.  grid (column tiles, heads, requests); a block of 128 threads owns 128 / LPC columns of one head's
-// matrix for one request, LPC lanes (a power of two) a column: lane `sub` holds the column's entries sub, sub + LPC, ... (R of
-// them, zero beyond dim) in registers.  In the memory form the matrix has one more column, n, whose "value" is 1 and whose
-// read-out n . q gives the token's divisor.  The tokens' keys, queries (times q_scale), values and gates pass through shared
-// memory in chunks of `tok` tokens; a column's sums are the lane's own entries in ascending order, then a butterfly over its
-// LPC lanes, whatever the chunk.
+// matrix for one request, LPC lanes (a power of two) a column: lane `sub` holds the column's entries sub R .. sub R + R - 1
+// (zero beyond dim) in registers, so that a token's key and query reach it as 16-byte reads of shared memory (the rows
+// there give every lane's piece four floats of padding: the pieces of the lanes that read together lie in different banks).
+// With few lanes a column a token costs a lane 2 R multiply-adds (3 R in the delta form) against R / 2 reads and a
+// butterfly of log2 LPC steps.  In the memory form the matrix has one more column, n, whose "value" is 1 and whose read-out
+// n . q gives the token's divisor.  The tokens' keys, queries (times q_scale), values and gates pass through shared memory
+// in chunks of `tok` tokens; a column's sums are the lane's own entries in four interleaved partial sums of ascending
+// order, then a butterfly over its LPC lanes, whatever the chunk.  While a chunk is walked, the next one is already on its
+// way from memory into registers (kScanFetch keys, queries and values a thread: a chunk holds at most 128 kScanFetch of
+// each), so that the walk waits for memory once a request and not once a chunk.
 constexpr int kScanThreads = 128;
 constexpr int kModeMemory = 0, kModeDelta = 1;
+constexpr int kPiecePad = 4;
+constexpr int kScanFetch = 16;
 
 template <typename T, int R, int MODE>
 __global__ void __launch_bounds__(kScanThreads)
@@ -113,10 +120,11 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
                    int vdim, int lpc_shift, int tok, float* __restrict__ y, float* __restrict__ bottom) {
   grid_dependency_wait();
   grid_dependency_launch();
-  extern __shared__ float matrix_smem[];
+  extern __shared__ __align__(16) float matrix_smem[];
   constexpr int G = MODE == kModeMemory ? 3 : 2;
+  constexpr int PIECE = R + kPiecePad;
   const int LPC = 1 << lpc_shift, cols_per_block = kScanThreads >> lpc_shift;
-  const int dim_pad = LPC * R;
+  const int row = LPC * PIECE;                                // floats of a token's key (or query) in shared memory
   const int columns = MODE == kModeMemory ? vdim + 1 : vdim;
   const int tid = threadIdx.x, cc = tid >> lpc_shift, sub = tid & (LPC - 1);
   const int col = blockIdx.x * cols_per_block + cc;
@@ -125,80 +133,146 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
   const int kv_head = head / (heads / kv_heads);
   const int q0 = query_start[request], q_len = query_start[request + 1] - q0;
   if (q_len <= 0) return;                                    // (the whole block)
-  float* ks = matrix_smem;                                    // [tok][dim_pad]
-  float* qs = ks + tok * dim_pad;                             // [tok][dim_pad]
-  float* vs = qs + tok * dim_pad;                             // [tok][cols_per_block]
+  float* ks = matrix_smem;                                    // [tok][row]
+  float* qs = ks + tok * row;                                 // [tok][row]
+  float* vs = qs + tok * row;                                 // [tok][cols_per_block]
   float* gs = vs + tok * cols_per_block;                      // [tok][4]
   float* kept = states + (long long)state_slots[request] * state_stride + state_offset + ((size_t)head * columns + (active ? col : 0)) * dim;
   float s[R];
+  // (a lane's piece as 16-byte accesses where it lies so: a column is `dim` floats, the state's row may start anywhere)
+  const bool wide = (dim & 3) == 0 && (reinterpret_cast<size_t>(kept) & 15) == 0;
+  if (wide) {
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = sub + LPC * r;
-    s[r] = (active && i < dim) ? kept[i] : 0.f;
+    for (int r = 0; r < R; r += 4) {
+      const int i = sub * R + r;
+      const float4 piece = (active && i < dim) ? *reinterpret_cast<const float4*>(kept + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s[r] = piece.x, s[r + 1] = piece.y, s[r + 2] = piece.z, s[r + 3] = piece.w;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = sub * R + r;
+      s[r] = (active && i < dim) ? kept[i] : 0.f;
+    }
   }
+  constexpr int LOG_R = R == 4 ? 2 : R == 8 ? 3 : R == 16 ? 4 : 5;
+  const int dim_shift = LOG_R + lpc_shift, dim_pad = 1 << dim_shift, col_shift = 7 - lpc_shift;
+  const T* k_head = k + k_col + kv_head * dim;
+  const T* q_head = q + q_col + kv_head * dim;
+  const T* v_head = v + v_col + head * vdim + blockIdx.x * cols_per_block;
+  const int cols_here = min(cols_per_block, vdim - (int)blockIdx.x * cols_per_block);      // value columns of this block (n is none)
+  T next_k[kScanFetch], next_q[kScanFetch], next_v[kScanFetch];
+  float next_g = 0.f;
+  auto fetch = [&](int t0) {
+    const int len = min(tok, q_len - t0);
+    const size_t first = (size_t)(q0 + t0);
+#pragma unroll
+    for (int j = 0; j < kScanFetch; ++j) {
+      const int idx = tid + kScanThreads * j, tt = idx >> dim_shift, i = idx & (dim_pad - 1);
+      const bool real = tt < len && i < dim;
+      next_k[j] = real ? k_head[(first + tt) * k_ld + i] : from_float<T>(0.f);
+      next_q[j] = real ? q_head[(first + tt) * q_ld + i] : from_float<T>(0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kScanFetch; ++j) {
+      const int idx = tid + kScanThreads * j, tt = idx >> col_shift, c = idx & (cols_per_block - 1);
+      next_v[j] = (tt < len && c < cols_here) ? v_head[(first + tt) * v_ld + c] : from_float<T>(1.f);      // (the column n)
+    }
+    if (tid < len * G) next_g = gates[((first + tid / G) * heads + head) * G + tid % G];
+  };
+  fetch(0);
   for (int t0 = 0; t0 < q_len; t0 += tok) {
     const int len = min(tok, q_len - t0);
     __syncthreads();                                          // the chunk before has been read
-    for (int idx = tid; idx < len * dim_pad; idx += kScanThreads) {
-      const int tt = idx / dim_pad, i = idx - tt * dim_pad;
-      const size_t token = (size_t)(q0 + t0 + tt);
-      const bool real = i < dim;
-      ks[idx] = real ? to_float(k[token * k_ld + k_col + kv_head * dim + i]) : 0.f;
-      qs[idx] = real ? q_scale * to_float(q[token * q_ld + q_col + kv_head * dim + i]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kScanFetch; ++j) {
+      const int idx = tid + kScanThreads * j, tt = idx >> dim_shift, i = idx & (dim_pad - 1);
+      if (tt < len) {
+        const int at = tt * row + (i >> LOG_R) * PIECE + (i & (R - 1));
+        ks[at] = to_float(next_k[j]);
+        qs[at] = q_scale * to_float(next_q[j]);
+      }
     }
-    for (int idx = tid; idx < len * cols_per_block; idx += kScanThreads) {
-      const int tt = idx / cols_per_block, c = blockIdx.x * cols_per_block + (idx - tt * cols_per_block);
-      const size_t token = (size_t)(q0 + t0 + tt);
-      vs[idx] = c < vdim ? to_float(v[token * v_ld + v_col + head * vdim + c]) : 1.f;      // (the column n)
+#pragma unroll
+    for (int j = 0; j < kScanFetch; ++j) {
+      const int idx = tid + kScanThreads * j;
+      if ((idx >> col_shift) < len) vs[idx] = to_float(next_v[j]);
     }
-    for (int idx = tid; idx < len * G; idx += kScanThreads) {
-      const int tt = idx / G, g = idx - tt * G;
-      gs[tt * 4 + g] = gates[((size_t)(q0 + t0 + tt) * heads + head) * G + g];
-    }
+    if (tid < len * G) gs[(tid / G) * 4 + tid % G] = next_g;
     __syncthreads();
+    if (t0 + tok < q_len) fetch(t0 + tok);
     for (int tt = 0; tt < len; ++tt) {
-      const float* kk = ks + tt * dim_pad + sub;
-      const float* qq = qs + tt * dim_pad + sub;
+      const float4* kk = reinterpret_cast<const float4*>(ks + tt * row + sub * PIECE);
+      const float4* qq = reinterpret_cast<const float4*>(qs + tt * row + sub * PIECE);
       const float value = vs[tt * cols_per_block + cc];
       const size_t token = (size_t)(q0 + t0 + tt);
-      float acc = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
       if (MODE == kModeMemory) {
         const float keep = gs[tt * 4], write = gs[tt * 4 + 1] * value;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          s[r] = keep * s[r] + write * kk[LPC * r];
-          acc += s[r] * qq[LPC * r];
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = kk[r >> 2], qv = qq[r >> 2];
+          s[r] = keep * s[r] + write * kv.x;
+          s[r + 1] = keep * s[r + 1] + write * kv.y;
+          s[r + 2] = keep * s[r + 2] + write * kv.z;
+          s[r + 3] = keep * s[r + 3] + write * kv.w;
+          acc[0] += s[r] * qv.x;
+          acc[1] += s[r + 1] * qv.y;
+          acc[2] += s[r + 2] * qv.z;
+          acc[3] += s[r + 3] * qv.w;
         }
       } else {
         const float decay = gs[tt * 4], beta = gs[tt * 4 + 1];
-        float seen = 0.f;
+        float seen[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = kk[r >> 2];
           s[r] *= decay;
-          seen += s[r] * kk[LPC * r];
+          s[r + 1] *= decay;
+          s[r + 2] *= decay;
+          s[r + 3] *= decay;
+          seen[0] += s[r] * kv.x;
+          seen[1] += s[r + 1] * kv.y;
+          seen[2] += s[r + 2] * kv.z;
+          seen[3] += s[r + 3] * kv.w;
         }
-        for (int o = LPC >> 1; o > 0; o >>= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
-        const float u = beta * (value - seen);
+        float total = (seen[0] + seen[1]) + (seen[2] + seen[3]);
+        for (int o = LPC >> 1; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        const float u = beta * (value - total);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          s[r] += kk[LPC * r] * u;
-          acc += s[r] * qq[LPC * r];
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = kk[r >> 2], qv = qq[r >> 2];
+          s[r] += kv.x * u;
+          s[r + 1] += kv.y * u;
+          s[r + 2] += kv.z * u;
+          s[r + 3] += kv.w * u;
+          acc[0] += s[r] * qv.x;
+          acc[1] += s[r + 1] * qv.y;
+          acc[2] += s[r + 2] * qv.z;
+          acc[3] += s[r + 3] * qv.w;
         }
       }
-      for (int o = LPC >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      float read = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      for (int o = LPC >> 1; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
       if (sub == 0 && active) {
         if (col < vdim) {
-          y[(token * heads + head) * vdim + col] = acc;
+          y[(token * heads + head) * vdim + col] = read;
         } else {
-          bottom[token * heads + head] = fmaxf(fabsf(acc), gs[tt * 4 + 2]) + 1e-6f;
+          bottom[token * heads + head] = fmaxf(fabsf(read), gs[tt * 4 + 2]) + 1e-6f;
         }
       }
     }
   }
-  if (active) {
+  if (active && wide) {
+#pragma unroll
+    for (int r = 0; r < R; r += 4) {
+      const int i = sub * R + r;
+      if (i < dim) *reinterpret_cast<float4*>(kept + i) = make_float4(s[r], s[r + 1], s[r + 2], s[r + 3]);
+    }
+  } else if (active) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const int i = sub + LPC * r;
+      const int i = sub * R + r;
       if (i < dim) kept[i] = s[r];
     }
   }
@@ -235,9 +309,15 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* 
   }
 }
 
-// grid (channel blocks, requests); a thread owns one channel and walks the request's tokens with the state in a register.
+// grid (channel blocks, requests); a block of sixteen warps owns 32 channels (a lane a channel) and walks the request's tokens
+// in tiles of 64, four tokens a warp, whose loads are issued together: one round trip to memory a tile.  What does not depend
+// on the state (both gates, the decay a, the token's input b = sqrt(1 - a^2) i u and the gelu branch) is computed by all
+// warps; a and b go to shared memory, where one warp walks the tile with S = a S + b, one fused multiply-add a token, whatever
+// the tile (so a sequence whole or in portions gives the same bits); all warps then multiply by their branch and store.
+constexpr int kRecChannels = 32, kRecTile = 64, kRecWarps = 16, kRecEach = kRecTile / kRecWarps;
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kRecWarps * 32)
 gated_recurrence_scan_kernel(const float* __restrict__ u, const float* __restrict__ pre, const float* __restrict__ gate_bias,
                              const float* __restrict__ rate, const T* __restrict__ proj, int ld, int y_col,
                              const float* __restrict__ y_bias, float* __restrict__ states, long long state_stride,
@@ -245,27 +325,59 @@ gated_recurrence_scan_kernel(const float* __restrict__ u, const float* __restric
                              int width, int n_tokens, T* __restrict__ out) {
   grid_dependency_wait();
   grid_dependency_launch();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x, request = blockIdx.y;
+  __shared__ float decay[kRecTile][kRecChannels];
+  __shared__ float carried[kRecTile][kRecChannels];           // b on the way in, S on the way out
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * kRecChannels + lane, request = blockIdx.y;
   const int q0 = query_start[request], q_len = query_start[request + 1] - q0;
-  if (c >= width || q_len <= 0) return;
-  float* kept = states + (long long)state_slots[request] * state_stride + state_offset + c;
-  const float r_bias = gate_bias[c], i_bias = gate_bias[width + c], slope = rate[c], branch_bias = y_bias ? y_bias[c] : 0.f;
-  const float* pre_r = pre + (size_t)q0 * width + c;
-  const float* pre_i = pre + ((size_t)n_tokens + q0) * width + c;
-  const float* input = u + (size_t)q0 * width + c;
-  const T* branch = proj + (size_t)q0 * ld + y_col + c;
-  T* dst = out + (size_t)q0 * width + c;
-  float state = *kept;
-#pragma unroll 4
-  for (int t = 0; t < q_len; ++t) {
-    const float r = sigmoid_f(pre_r[(size_t)t * width] + r_bias);
-    const float gate_in = sigmoid_f(pre_i[(size_t)t * width] + i_bias);
-    const float log_a = slope * r;
-    const float a = expf(log_a), spread = sqrtf(-expm1f(2.f * log_a));       // sqrt(1 - a^2) without cancellation
-    state = a * state + spread * (gate_in * input[(size_t)t * width]);
-    dst[(size_t)t * width] = from_float<T>(state * gelu_tanh_f(to_float(branch[(size_t)t * ld]) + branch_bias));
+  if (q_len <= 0) return;                                     // (the whole block)
+  const bool real = c < width;
+  const int cc = real ? c : 0;
+  float* kept = states + (long long)state_slots[request] * state_stride + state_offset + cc;
+  const float r_bias = gate_bias[cc], i_bias = gate_bias[width + cc], slope = rate[cc], branch_bias = y_bias ? y_bias[cc] : 0.f;
+  const float* pre_r = pre + (size_t)q0 * width + cc;
+  const float* pre_i = pre + ((size_t)n_tokens + q0) * width + cc;
+  const float* input = u + (size_t)q0 * width + cc;
+  const T* branch = proj + (size_t)q0 * ld + y_col + cc;
+  T* dst = out + (size_t)q0 * width + cc;
+  float state = warp == 0 ? *kept : 0.f;
+  for (int t0 = 0; t0 < q_len; t0 += kRecTile) {
+    const int len = min(kRecTile, q_len - t0);
+    float pr[kRecEach], pi[kRecEach], in[kRecEach], br[kRecEach];
+#pragma unroll
+    for (int e = 0; e < kRecEach; ++e) {                      // (a token beyond the tile reads the tile's first again)
+      const int tt = warp + e * kRecWarps;
+      const size_t t = (size_t)(t0 + (tt < len ? tt : 0));
+      pr[e] = pre_r[t * width], pi[e] = pre_i[t * width], in[e] = input[t * width], br[e] = to_float(branch[t * ld]);
+    }
+#pragma unroll
+    for (int e = 0; e < kRecEach; ++e) {
+      const int tt = warp + e * kRecWarps;
+      const float r = sigmoid_f(pr[e] + r_bias);
+      const float gate_in = sigmoid_f(pi[e] + i_bias);
+      const float log_a = slope * r;
+      const float spread = sqrtf(-expm1f(2.f * log_a));       // sqrt(1 - a^2) without cancellation
+      decay[tt][lane] = expf(log_a);
+      carried[tt][lane] = spread * (gate_in * in[e]);
+      br[e] = gelu_tanh_f(br[e] + branch_bias);
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll 8
+      for (int tt = 0; tt < len; ++tt) {
+        state = fmaf(decay[tt][lane], state, carried[tt][lane]);
+        carried[tt][lane] = state;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < kRecEach; ++e) {
+      const int tt = warp + e * kRecWarps;
+      if (real && tt < len) dst[(size_t)(t0 + tt) * width] = from_float<T>(carried[tt][lane] * br[e]);
+    }
+    __syncthreads();                                          // the next tile writes what this one read
   }
-  *kept = state;
+  if (warp == 0 && real) *kept = state;
 }
 
 }  // namespace ms
@@ -328,16 +440,24 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
              heads, kv_heads, dim, vdim);
   MS_REQUIRE(mode != kModeMemory || bottom != nullptr, "matrix_scan: the memory form writes the tokens' divisors");
   MS_REQUIRE(heads <= 65535 && n_requests <= 65535, "matrix_scan: grid %d x %d exceeds the launch limits", heads, n_requests);
-  // lanes per column: aim at eight entries a lane; sixteen where a warp would not hold the column otherwise
+  // lanes per column: as few as hold the column in 32 entries a lane (more columns a block then share a token's key and
+  // query), the lane's piece rounded up to 4, 8, 16 or 32; one more doubling of the lanes where that wastes less
   int lpc_shift = 0;
-  while (lpc_shift < 5 && (dim + (1 << lpc_shift) - 1) / (1 << lpc_shift) > 8) ++lpc_shift;
-  const int per_lane = (dim + (1 << lpc_shift) - 1) >> lpc_shift;
-  const int r = per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : 16;
+  while (lpc_shift < 5 && (dim + (1 << lpc_shift) - 1) / (1 << lpc_shift) > 32) ++lpc_shift;
+  auto piece = [&](int shift) {
+    const int per_lane = (dim + (1 << shift) - 1) >> shift;
+    return per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : per_lane <= 16 ? 16 : 32;
+  };
+  while (lpc_shift < 3 && (piece(lpc_shift + 1) << (lpc_shift + 1)) < (piece(lpc_shift) << lpc_shift)) ++lpc_shift;
+  const int r = piece(lpc_shift);
   const int cols_per_block = kScanThreads >> lpc_shift;
   const int columns = mode == kModeMemory ? vdim + 1 : vdim;
-  const int row_floats = 2 * (r << lpc_shift) + cols_per_block + 4;
+  const int row_floats = 2 * ((r + kPiecePad) << lpc_shift) + cols_per_block + 4;
+  // a chunk: at most 16 tokens, 128 kScanFetch keys (what the threads hold of the next chunk) and 40 KB of shared memory
   int tok = max_query_len < 16 ? max_query_len : 16;
-  while (tok > 1 && (size_t)tok * row_floats * sizeof(float) > 40 * 1024) tok >>= 1;
+  while (tok > 1 && ((size_t)tok * row_floats * sizeof(float) > 40 * 1024 || (tok * r << lpc_shift) > kScanThreads * kScanFetch)) tok >>= 1;
+  MS_REQUIRE((tok * r << lpc_shift) <= kScanThreads * kScanFetch && tok * cols_per_block <= kScanThreads * kScanFetch,
+             "matrix_scan: a chunk of %d tokens of %d entries does not fit the threads' registers", tok, r << lpc_shift);
   const size_t smem = (size_t)tok * row_floats * sizeof(float);
   dim3 grid((columns + cols_per_block - 1) / cols_per_block, heads, n_requests);
 #define MS_MATRIX_SCAN(R, MODE)                                                                                               \
@@ -346,9 +466,11 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
                                      state_offset, state_slots, query_start, heads, kv_heads, dim, vdim, lpc_shift, tok, y,     \
                                      bottom)))
   if (mode == kModeMemory) {
-    if (r == 4) { MS_MATRIX_SCAN(4, kModeMemory); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeMemory); } else { MS_MATRIX_SCAN(16, kModeMemory); }
+    if (r == 4) { MS_MATRIX_SCAN(4, kModeMemory); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeMemory); }
+    else if (r == 16) { MS_MATRIX_SCAN(16, kModeMemory); } else { MS_MATRIX_SCAN(32, kModeMemory); }
   } else {
-    if (r == 4) { MS_MATRIX_SCAN(4, kModeDelta); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeDelta); } else { MS_MATRIX_SCAN(16, kModeDelta); }
+    if (r == 4) { MS_MATRIX_SCAN(4, kModeDelta); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeDelta); }
+    else if (r == 16) { MS_MATRIX_SCAN(16, kModeDelta); } else { MS_MATRIX_SCAN(32, kModeDelta); }
   }
 #undef MS_MATRIX_SCAN
   MS_CHECK_LAUNCH("matrix_scan");
@@ -382,8 +504,8 @@ MS_EXPORT int ms_gated_recurrence_scan(const float* u, const float* pre, const f
                                        cudaStream_t stream) {
   if (n_requests == 0 || n_tokens == 0 || width == 0) return 0;
   MS_REQUIRE(n_requests <= 65535, "gated_recurrence_scan: %d requests exceed the launch limits", n_requests);
-  dim3 grid((width + 127) / 128, n_requests);
-  MS_REC_DISPATCH(dtype, (ms::launch(gated_recurrence_scan_kernel<T>, grid, 128, 0, stream, u, pre, gate_bias, rate, (const T*)proj,
+  dim3 grid((width + kRecChannels - 1) / kRecChannels, n_requests);
+  MS_REC_DISPATCH(dtype, (ms::launch(gated_recurrence_scan_kernel<T>, grid, kRecWarps * 32, 0, stream, u, pre, gate_bias, rate, (const T*)proj,
                                      ld, y_col, y_bias, states, state_stride, state_offset, state_slots, query_start, width,
                                      n_tokens, (T*)out)));
   MS_CHECK_LAUNCH("gated_recurrence_scan");

@@ -71,7 +71,7 @@ def build_runtime(model_dir: Union[str, Path, None], engine_config: Optional[Eng
     spec = architecture.build_spec(config)
     model = DecoderModel(spec, dtype, device)
     if model_dir is not None:
-        tied = [(name, spec.embedding_name) for name in spec.optional_names] if spec.output_name is None else []
+        tied = [(name, spec.embedding_name) for name in spec.tied_copies] if spec.output_name is None else []
         tensors, report = load_tensors(model_dir, model.param_specs(), dtype, device, spec.optional_names, tied)
     else:
         tensors, report = random_tensors_on_device(model.param_specs(), weights_seed or 0, dtype, device), None

@@ -63,8 +63,12 @@ class ModelSpec:
     # True where the architecture has no position limit of its own and `max_positions` is only the engine's bound:
     # without an explicit `max_model_len` a runtime then takes the size of its page pool as the limit.
     nominal_max_positions: bool = False
-    # Names that may be present in a checkpoint without being used (a stored copy of a tied matrix).
+    # Names that may be present in a checkpoint without being used (a stored copy of a tied matrix, the norm of a
+    # feed-forward that a layer does not have).
     optional_names: Sequence[str] = ()
+    # Those of `optional_names` that are stored copies of the tied output matrix: where present they must equal the
+    # embedding table bit for bit.
+    tied_copies: Sequence[str] = ()
     # The frame around the layers: embeddings are multiplied by `embedding_scale` as they enter the residual
     # stream; logits are multiplied by `logit_scale` and then, with `logit_softcap` c, become c * tanh(logit / c).
     embedding_scale: float = 1.0
