@@ -95,7 +95,7 @@ __global__ void decay_gates_kernel(const float* __restrict__ logits, const float
   gates[2 * i + 1] = sigmoid_f(row[head]);
 }
 
-// The matrix recurrence.  grid (column tiles, heads, requests); a block of 128 threads owns 128 / LPC columns of one head's
+// The matrix recurrence.  grid (column tiles, heads, requests); a block of 256 threads owns 256 / LPC columns of one head's
 // matrix for one request, LPC lanes (a power of two) a column: lane `sub` holds the column's entries sub R .. sub R + R - 1
 // (zero beyond dim) in registers, so that a token's key and query reach it as 16-byte reads of shared memory (the rows
 // there give every lane's piece four floats of padding: the pieces of the lanes that read together lie in different banks).
@@ -104,12 +104,22 @@ __global__ void decay_gates_kernel(const float* __restrict__ logits, const float
 // n . q gives the token's divisor.  The tokens' keys, queries (times q_scale), values and gates pass through shared memory
 // in chunks of `tok` tokens; a column's sums are the lane's own entries in four interleaved partial sums of ascending
 // order, then a butterfly over its LPC lanes, whatever the chunk.  While a chunk is walked, the next one is already on its
-// way from memory into registers (kScanFetch keys, queries and values a thread: a chunk holds at most 128 kScanFetch of
+// way from memory into registers (kScanFetch keys, queries and values a thread: a chunk holds at most 256 kScanFetch of
 // each), so that the walk waits for memory once a request and not once a chunk.
-constexpr int kScanThreads = 128;
+constexpr int kScanThreads = 256, kScanShift = 8;
 constexpr int kModeMemory = 0, kModeDelta = 1;
 constexpr int kPiecePad = 4;
-constexpr int kScanFetch = 16;
+constexpr int kScanFetch = 8;
+
+// The sum over the 2^shift lanes of a column (a butterfly from the widest step down; `shift` is the same in the whole block).
+__device__ __forceinline__ float column_sum(float v, int shift) {
+  if (shift > 4) v += __shfl_xor_sync(0xffffffffu, v, 16);
+  if (shift > 3) v += __shfl_xor_sync(0xffffffffu, v, 8);
+  if (shift > 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
+  if (shift > 1) v += __shfl_xor_sync(0xffffffffu, v, 2);
+  if (shift > 0) v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v;
+}
 
 template <typename T, int R, int MODE>
 __global__ void __launch_bounds__(kScanThreads)
@@ -156,11 +166,15 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
     }
   }
   constexpr int LOG_R = R == 4 ? 2 : R == 8 ? 3 : R == 16 ? 4 : 5;
-  const int dim_shift = LOG_R + lpc_shift, dim_pad = 1 << dim_shift, col_shift = 7 - lpc_shift;
+  const int dim_shift = LOG_R + lpc_shift, dim_pad = 1 << dim_shift, col_shift = kScanShift - lpc_shift;
   const T* k_head = k + k_col + kv_head * dim;
   const T* q_head = q + q_col + kv_head * dim;
   const T* v_head = v + v_col + head * vdim + blockIdx.x * cols_per_block;
   const int cols_here = min(cols_per_block, vdim - (int)blockIdx.x * cols_per_block);      // value columns of this block (n is none)
+  // where this lane writes: a value column's read-out into y, the column n's into the tokens' divisors; one step a token
+  const bool is_n = MODE == kModeMemory && col == vdim;
+  float* out_at = (sub == 0 && active) ? (is_n ? bottom + (size_t)q0 * heads + head : y + ((size_t)q0 * heads + head) * vdim + col) : nullptr;
+  const size_t out_step = is_n ? (size_t)heads : (size_t)heads * vdim;
   T next_k[kScanFetch], next_q[kScanFetch], next_v[kScanFetch];
   float next_g = 0.f;
   auto fetch = [&](int t0) {
@@ -201,14 +215,15 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
     if (tid < len * G) gs[(tid / G) * 4 + tid % G] = next_g;
     __syncthreads();
     if (t0 + tok < q_len) fetch(t0 + tok);
+#pragma unroll 2
     for (int tt = 0; tt < len; ++tt) {
       const float4* kk = reinterpret_cast<const float4*>(ks + tt * row + sub * PIECE);
       const float4* qq = reinterpret_cast<const float4*>(qs + tt * row + sub * PIECE);
       const float value = vs[tt * cols_per_block + cc];
-      const size_t token = (size_t)(q0 + t0 + tt);
+      const float4 gate = reinterpret_cast<const float4*>(gs)[tt];
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       if (MODE == kModeMemory) {
-        const float keep = gs[tt * 4], write = gs[tt * 4 + 1] * value;
+        const float keep = gate.x, write = gate.y * value;
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
           const float4 kv = kk[r >> 2], qv = qq[r >> 2];
@@ -222,7 +237,7 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
           acc[3] += s[r + 3] * qv.w;
         }
       } else {
-        const float decay = gs[tt * 4], beta = gs[tt * 4 + 1];
+        const float decay = gate.x, beta = gate.y;
         float seen[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
@@ -237,7 +252,7 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
           seen[3] += s[r + 3] * kv.w;
         }
         float total = (seen[0] + seen[1]) + (seen[2] + seen[3]);
-        for (int o = LPC >> 1; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        total = column_sum(total, lpc_shift);
         const float u = beta * (value - total);
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
@@ -253,13 +268,10 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
         }
       }
       float read = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      for (int o = LPC >> 1; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-      if (sub == 0 && active) {
-        if (col < vdim) {
-          y[(token * heads + head) * vdim + col] = read;
-        } else {
-          bottom[token * heads + head] = fmaxf(fabsf(read), gs[tt * 4 + 2]) + 1e-6f;
-        }
+      read = column_sum(read, lpc_shift);
+      if (out_at != nullptr) {
+        *out_at = is_n ? fmaxf(fabsf(read), gate.z) + 1e-6f : read;
+        out_at += out_step;
       }
     }
   }
@@ -426,6 +438,16 @@ MS_EXPORT int ms_decay_gates(const float* logits, const float* a_log, const floa
   return 0;
 }
 
+static int scan_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+    count = sms;
+  }
+  return count;
+}
+
 // mode 0 (memory): gates [tokens, heads, 3], state [heads, vdim + 1, dim] per slot, bottom [tokens, heads];
 // mode 1 (delta): gates [tokens, heads, 2], state [heads, vdim, dim], bottom unused.  q, k, v: rows of q_ld, k_ld, v_ld
 // numbers of type `dtype`; y float32 [tokens, heads, vdim].  max_query_len: an upper bound of the tokens a request brings.
@@ -440,8 +462,11 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
              heads, kv_heads, dim, vdim);
   MS_REQUIRE(mode != kModeMemory || bottom != nullptr, "matrix_scan: the memory form writes the tokens' divisors");
   MS_REQUIRE(heads <= 65535 && n_requests <= 65535, "matrix_scan: grid %d x %d exceeds the launch limits", heads, n_requests);
-  // lanes per column: as few as hold the column in 32 entries a lane (more columns a block then share a token's key and
-  // query), the lane's piece rounded up to 4, 8, 16 or 32; one more doubling of the lanes where that wastes less
+  // lanes per column: at least as many as hold the column in 32 entries a lane, the lane's piece rounded up to 4, 8, 16 or 32
+  // (one more doubling of the lanes where that wastes less).  Few lanes a column make the most of a token's key and query
+  // in shared memory, and suit a launch that fills the GPU anyway (many requests).  A launch of few requests is a chain of
+  // tokens whose length is what a warp does for one token: there the lanes are doubled (shorter pieces, more warps) while
+  // the launch stays under eight warps a multiprocessor.
   int lpc_shift = 0;
   while (lpc_shift < 5 && (dim + (1 << lpc_shift) - 1) / (1 << lpc_shift) > 32) ++lpc_shift;
   auto piece = [&](int shift) {
@@ -449,13 +474,22 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
     return per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : per_lane <= 16 ? 16 : 32;
   };
   while (lpc_shift < 3 && (piece(lpc_shift + 1) << (lpc_shift + 1)) < (piece(lpc_shift) << lpc_shift)) ++lpc_shift;
+  const long long all_columns = (long long)(mode == kModeMemory ? vdim + 1 : vdim);
+  auto warps_of = [&](int shift) {
+    const int per_block = kScanThreads >> shift;
+    return (long long)n_requests * heads * ((all_columns + per_block - 1) / per_block) * (kScanThreads / 32);
+  };
+  const long long room = 8LL * scan_sm_count();
+  while (lpc_shift < 5 && piece(lpc_shift) > 4 && warps_of(lpc_shift + 1) <= room) ++lpc_shift;
   const int r = piece(lpc_shift);
   const int cols_per_block = kScanThreads >> lpc_shift;
   const int columns = mode == kModeMemory ? vdim + 1 : vdim;
   const int row_floats = 2 * ((r + kPiecePad) << lpc_shift) + cols_per_block + 4;
-  // a chunk: at most 16 tokens, 128 kScanFetch keys (what the threads hold of the next chunk) and 40 KB of shared memory
+  // a chunk: at most 16 tokens, kScanThreads kScanFetch keys and as many values (what the threads hold of the next chunk)
+  // and 40 KB of shared memory
   int tok = max_query_len < 16 ? max_query_len : 16;
-  while (tok > 1 && ((size_t)tok * row_floats * sizeof(float) > 40 * 1024 || (tok * r << lpc_shift) > kScanThreads * kScanFetch)) tok >>= 1;
+  while (tok > 1 && ((size_t)tok * row_floats * sizeof(float) > 40 * 1024 || (tok * r << lpc_shift) > kScanThreads * kScanFetch ||
+                     tok * cols_per_block > kScanThreads * kScanFetch)) tok >>= 1;
   MS_REQUIRE((tok * r << lpc_shift) <= kScanThreads * kScanFetch && tok * cols_per_block <= kScanThreads * kScanFetch,
              "matrix_scan: a chunk of %d tokens of %d entries does not fit the threads' registers", tok, r << lpc_shift);
   const size_t smem = (size_t)tok * row_floats * sizeof(float);
