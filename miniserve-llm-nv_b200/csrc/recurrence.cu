@@ -215,7 +215,7 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
     if (tid < len * G) gs[(tid / G) * 4 + tid % G] = next_g;
     __syncthreads();
     if (t0 + tok < q_len) fetch(t0 + tok);
-#pragma unroll 2
+#pragma unroll 4
     for (int tt = 0; tt < len; ++tt) {
       const float4* kk = reinterpret_cast<const float4*>(ks + tt * row + sub * PIECE);
       const float4* qq = reinterpret_cast<const float4*>(qs + tt * row + sub * PIECE);

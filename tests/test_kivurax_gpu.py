@@ -163,6 +163,59 @@ def test_matrix_scan_kernel(dtype, mode, heads, kv_heads, dim, vdim):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mode", ["memory", "delta"])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 128, 64), (2, 2, 24, 40), (3, 3, 64, 20), (2, 1, 200, 8), (8, 8, 12, 6)])
+def test_matrix_scan_kernel_in_launches_that_fill_the_gpu(dtype, mode, heads, kv_heads, dim, vdim):
+    """The kernel gives a column fewer lanes (and a lane a longer piece of it) when a launch has many requests than when it
+    has few.  Four hundred requests of one to three tokens, their slots shuffled, take the forms that the test above does
+    not reach; the same requests a few at a time must agree with them to rounding."""
+    from miniserve_b200 import kernels
+
+    if mode == "memory":
+        kv_heads = heads
+    count = 400
+    lengths = [1 + (7 * i) % 3 for i in range(count)]
+    slots = torch.randperm(count, generator=torch.Generator().manual_seed(31)).tolist()
+    n, columns, G = sum(lengths), (vdim + 1 if mode == "memory" else vdim), (3 if mode == "memory" else 2)
+    proj = rand((n, 2 * kv_heads * dim + heads * vdim), dtype, 32, 0.5)
+    q_col, k_col, v_col = 0, kv_heads * dim, 2 * kv_heads * dim
+    if mode == "delta":
+        keys = proj[:, k_col:v_col].float().view(n, kv_heads, dim)
+        proj[:, k_col:v_col] = (keys / keys.norm(dim=-1, keepdim=True)).reshape(n, -1).to(dtype)
+    gates = torch.rand((n, heads, G), generator=torch.Generator().manual_seed(33)).cuda()
+    states = rand((count, heads * columns * dim), torch.float32, 34, 0.3)
+    start_states = states.clone()
+    y = torch.zeros((n, heads, vdim), dtype=torch.float32).cuda()
+    bottom = torch.zeros((n, heads), dtype=torch.float32).cuda() if mode == "memory" else None
+    kernels.matrix_scan(mode, proj, q_col, proj, k_col, proj, v_col, gates, states, 0, ints(slots), starts_of(lengths), max(lengths),
+                        heads, kv_heads, dim, vdim, y, q_scale=0.6, bottom=bottom)
+    expected_states = cpu(start_states)
+    expected_y, expected_bottom = torch.zeros(n, heads, vdim), torch.zeros(n, heads)
+    plain_ops.matrix_scan(mode, cpu(proj), q_col, cpu(proj), k_col, cpu(proj), v_col, cpu(gates), expected_states, 0, torch.tensor(slots),
+                          cpu(starts_of(lengths)), max(lengths), heads, kv_heads, dim, vdim, expected_y, q_scale=0.6, bottom=expected_bottom)
+    scale = max(1.0, float(expected_y.abs().max()))
+    assert torch.allclose(y.cpu(), expected_y, atol=2e-5 * scale, rtol=1e-4)
+    assert torch.allclose(states.cpu(), expected_states, atol=2e-5 * scale, rtol=1e-4)
+    if mode == "memory":
+        assert torch.allclose(bottom.cpu(), expected_bottom, atol=2e-5 * scale, rtol=1e-4)
+    # three requests at a time (a launch of few requests): the same rows and states to rounding
+    again, starts = start_states.clone(), [0]
+    for length in lengths:
+        starts.append(starts[-1] + length)
+    for first in range(0, 12, 3):
+        some = list(range(first, first + 3))
+        rows = torch.cat([torch.arange(starts[i], starts[i + 1]) for i in some]).cuda()
+        y_some = torch.zeros((rows.numel(), heads, vdim), dtype=torch.float32).cuda()
+        bottom_some = torch.zeros((rows.numel(), heads), dtype=torch.float32).cuda() if mode == "memory" else None
+        kernels.matrix_scan(mode, proj[rows].contiguous(), q_col, proj[rows].contiguous(), k_col, proj[rows].contiguous(), v_col,
+                            gates[rows].contiguous(), again, 0, ints([slots[i] for i in some]), starts_of([lengths[i] for i in some]),
+                            max(lengths[i] for i in some), heads, kv_heads, dim, vdim, y_some, q_scale=0.6, bottom=bottom_some)
+        assert torch.allclose(y_some, y[rows], atol=2e-5 * scale, rtol=1e-4)
+        for i in some:
+            assert torch.allclose(again[slots[i]], states[slots[i]], atol=2e-5 * scale, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,vdim,shared,divide,activation", [(4, 40, False, True, "sigmoid"), (4, 24, True, False, "silu"), (1, 10, False, True, "sigmoid"),
                                                                  (1, 14, True, False, "silu"), (5, 6, True, False, "silu"), (3, 130, False, True, "silu"),
                                                                  (2, 1, True, False, "sigmoid")])
