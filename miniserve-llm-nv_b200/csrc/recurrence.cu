@@ -290,12 +290,17 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
   }
 }
 
-// One warp per (token, head): v = y / bottom, v / sqrt(mean(v^2) + eps) * weight * act(gate).
+// One warp per (token, head): v = y / bottom, v / sqrt(mean(v^2) + eps) * weight * act(gate).  Where a head's row is
+// at most 512 numbers, a multiple of four, and lies on 16-byte boundaries in all four arrays (`wide`), a lane keeps its
+// four-number pieces in registers between the sum and the output and every access is one piece; otherwise number by number.
+template <typename T> struct alignas(sizeof(T) * 4) Four { T v[4]; };
+constexpr int kHeadPieces = 4;                               // pieces of four numbers a lane
+
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* __restrict__ bottom,
                                       const float* __restrict__ weight, int weight_per_head, const T* __restrict__ gate,
                                       int gate_ld, int gate_col, int activation, float eps, T* __restrict__ out, int n_tokens,
-                                      int heads, int vdim) {
+                                      int heads, int vdim, int wide) {
   grid_dependency_wait();
   grid_dependency_launch();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -305,15 +310,49 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* 
   const int head = (int)(item % heads);
   const float* row = y + (size_t)item * vdim;
   const float divisor = bottom ? bottom[item] : 1.f;
+  const float* w = weight + (weight_per_head ? (size_t)head * vdim : 0);
+  const T* z = gate + token * gate_ld + gate_col + (size_t)head * vdim;
+  T* dst = out + (token * heads + head) * vdim;
+  if (wide) {
+    const int pieces = vdim >> 2;
+    float4 value[kHeadPieces];
+    Four<T> g[kHeadPieces];
+    float sum_sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kHeadPieces; ++j) {
+      const int at = lane + 32 * j;
+      value[j] = at < pieces ? reinterpret_cast<const float4*>(row)[at] : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (at < pieces) g[j] = reinterpret_cast<const Four<T>*>(z)[at];
+    }
+#pragma unroll
+    for (int j = 0; j < kHeadPieces; ++j) {
+      value[j].x /= divisor, value[j].y /= divisor, value[j].z /= divisor, value[j].w /= divisor;
+      sum_sq += (value[j].x * value[j].x + value[j].y * value[j].y) + (value[j].z * value[j].z + value[j].w * value[j].w);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)vdim + eps);
+#pragma unroll
+    for (int j = 0; j < kHeadPieces; ++j) {
+      const int at = lane + 32 * j;
+      if (at < pieces) {
+        const float4 scale = reinterpret_cast<const float4*>(w)[at];
+        const float v4[4] = {value[j].x * inv * scale.x, value[j].y * inv * scale.y, value[j].z * inv * scale.z, value[j].w * inv * scale.w};
+        Four<T> o;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float gv = to_float(g[j].v[e]);
+          o.v[e] = from_float<T>(v4[e] * (activation ? gv * sigmoid_f(gv) : sigmoid_f(gv)));
+        }
+        reinterpret_cast<Four<T>*>(dst)[at] = o;
+      }
+    }
+    return;
+  }
   float sum_sq = 0.f;
   for (int c = lane; c < vdim; c += 32) {
     const float value = row[c] / divisor;
     sum_sq += value * value;
   }
   const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)vdim + eps);
-  const float* w = weight + (weight_per_head ? (size_t)head * vdim : 0);
-  const T* z = gate + token * gate_ld + gate_col + (size_t)head * vdim;
-  T* dst = out + (token * heads + head) * vdim;
   for (int c = lane; c < vdim; c += 32) {
     const float g = to_float(z[c]);
     const float factor = activation ? g * sigmoid_f(g) : sigmoid_f(g);
@@ -322,7 +361,7 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* 
 }
 
 // grid (channel blocks, requests); a block of sixteen warps owns 32 channels (a lane a channel) and walks the request's tokens
-// in tiles of 64, four tokens a warp, whose loads are issued together: one round trip to memory a tile.  What does not depend
+// in tiles of 64, four tokens a warp, whose loads are issued together, a tile ahead of the walk.  What does not depend
 // on the state (both gates, the decay a, the token's input b = sqrt(1 - a^2) i u and the gelu branch) is computed by all
 // warps; a and b go to shared memory, where one warp walks the tile with S = a S + b, one fused multiply-add a token, whatever
 // the tile (so a sequence whole or in portions gives the same bits); all warps then multiply by their branch and store.
@@ -353,15 +392,21 @@ gated_recurrence_scan_kernel(const float* __restrict__ u, const float* __restric
   const T* branch = proj + (size_t)q0 * ld + y_col + cc;
   T* dst = out + (size_t)q0 * width + cc;
   float state = warp == 0 ? *kept : 0.f;
-  for (int t0 = 0; t0 < q_len; t0 += kRecTile) {
+  float pr[kRecEach], pi[kRecEach], in[kRecEach];           // the next tile's inputs, on their way (as loaded: no
+  T br[kRecEach];                                             // arithmetic waits for them before the walk)
+  auto fetch = [&](int t0) {
     const int len = min(kRecTile, q_len - t0);
-    float pr[kRecEach], pi[kRecEach], in[kRecEach], br[kRecEach];
 #pragma unroll
     for (int e = 0; e < kRecEach; ++e) {                      // (a token beyond the tile reads the tile's first again)
       const int tt = warp + e * kRecWarps;
       const size_t t = (size_t)(t0 + (tt < len ? tt : 0));
-      pr[e] = pre_r[t * width], pi[e] = pre_i[t * width], in[e] = input[t * width], br[e] = to_float(branch[t * ld]);
+      pr[e] = pre_r[t * width], pi[e] = pre_i[t * width], in[e] = input[t * width], br[e] = branch[t * ld];
     }
+  };
+  fetch(0);
+  for (int t0 = 0; t0 < q_len; t0 += kRecTile) {
+    const int len = min(kRecTile, q_len - t0);
+    float gelu[kRecEach];
 #pragma unroll
     for (int e = 0; e < kRecEach; ++e) {
       const int tt = warp + e * kRecWarps;
@@ -371,9 +416,10 @@ gated_recurrence_scan_kernel(const float* __restrict__ u, const float* __restric
       const float spread = sqrtf(-expm1f(2.f * log_a));       // sqrt(1 - a^2) without cancellation
       decay[tt][lane] = expf(log_a);
       carried[tt][lane] = spread * (gate_in * in[e]);
-      br[e] = gelu_tanh_f(br[e] + branch_bias);
+      gelu[e] = gelu_tanh_f(to_float(br[e]) + branch_bias);
     }
     __syncthreads();
+    if (t0 + kRecTile < q_len) fetch(t0 + kRecTile);
     if (warp == 0) {
 #pragma unroll 8
       for (int tt = 0; tt < len; ++tt) {
@@ -385,7 +431,7 @@ gated_recurrence_scan_kernel(const float* __restrict__ u, const float* __restric
 #pragma unroll
     for (int e = 0; e < kRecEach; ++e) {
       const int tt = warp + e * kRecWarps;
-      if (real && tt < len) dst[(size_t)(t0 + tt) * width] = from_float<T>(carried[tt][lane] * br[e]);
+      if (real && tt < len) dst[(size_t)(t0 + tt) * width] = from_float<T>(carried[tt][lane] * gelu[e]);
     }
     __syncthreads();                                          // the next tile writes what this one read
   }
@@ -521,9 +567,13 @@ MS_EXPORT int ms_head_norm_gate(const float* y, const float* bottom, const float
   const int warps = 4;
   const long long blocks = ((long long)n_tokens * heads + warps - 1) / warps;
   MS_REQUIRE(blocks < 2147483647LL, "head_norm_gate: %lld heads in one launch is too many", (long long)n_tokens * heads);
+  const size_t element = dtype == MS_F32 ? 4 : 2;
+  const int wide = vdim % 4 == 0 && vdim <= 128 * kHeadPieces && gate_ld % 4 == 0 && gate_col % 4 == 0 &&
+                   reinterpret_cast<size_t>(y) % 16 == 0 && reinterpret_cast<size_t>(weight) % 16 == 0 &&
+                   reinterpret_cast<size_t>(gate) % (4 * element) == 0 && reinterpret_cast<size_t>(out) % (4 * element) == 0;
   MS_REC_DISPATCH(dtype, (ms::launch(head_norm_gate_kernel<T>, (unsigned)blocks, warps * 32, 0, stream, y, bottom, weight,
                                      weight_per_head, (const T*)gate, gate_ld, gate_col, activation, eps, (T*)out, n_tokens,
-                                     heads, vdim)));
+                                     heads, vdim, wide)));
   MS_CHECK_LAUNCH("head_norm_gate");
   return 0;
 }
