@@ -304,59 +304,60 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* 
   grid_dependency_wait();
   grid_dependency_launch();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * warps + warp;
-  if (item >= (long long)n_tokens * heads) return;
-  const size_t token = (size_t)(item / heads);
-  const int head = (int)(item % heads);
-  const float* row = y + (size_t)item * vdim;
-  const float divisor = bottom ? bottom[item] : 1.f;
-  const float* w = weight + (weight_per_head ? (size_t)head * vdim : 0);
-  const T* z = gate + token * gate_ld + gate_col + (size_t)head * vdim;
-  T* dst = out + (token * heads + head) * vdim;
-  if (wide) {
-    const int pieces = vdim >> 2;
-    float4 value[kHeadPieces];
-    Four<T> g[kHeadPieces];
-    float sum_sq = 0.f;
+  const long long items = (long long)n_tokens * heads;
+  for (long long item = (long long)blockIdx.x * warps + warp; item < items; item += (long long)gridDim.x * warps) {
+    const size_t token = (size_t)(item / heads);
+    const int head = (int)(item % heads);
+    const float* row = y + (size_t)item * vdim;
+    const float divisor = bottom ? bottom[item] : 1.f;
+    const float* w = weight + (weight_per_head ? (size_t)head * vdim : 0);
+    const T* z = gate + token * gate_ld + gate_col + (size_t)head * vdim;
+    T* dst = out + (token * heads + head) * vdim;
+    if (wide) {
+      const int pieces = vdim >> 2;
+      float4 value[kHeadPieces];
+      Four<T> g[kHeadPieces];
+      float sum_sq = 0.f;
 #pragma unroll
-    for (int j = 0; j < kHeadPieces; ++j) {
-      const int at = lane + 32 * j;
-      value[j] = at < pieces ? reinterpret_cast<const float4*>(row)[at] : make_float4(0.f, 0.f, 0.f, 0.f);
-      if (at < pieces) g[j] = reinterpret_cast<const Four<T>*>(z)[at];
+      for (int j = 0; j < kHeadPieces; ++j) {
+        const int at = lane + 32 * j;
+        value[j] = at < pieces ? reinterpret_cast<const float4*>(row)[at] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (at < pieces) g[j] = reinterpret_cast<const Four<T>*>(z)[at];
+      }
+#pragma unroll
+      for (int j = 0; j < kHeadPieces; ++j) {
+        value[j].x /= divisor, value[j].y /= divisor, value[j].z /= divisor, value[j].w /= divisor;
+        sum_sq += (value[j].x * value[j].x + value[j].y * value[j].y) + (value[j].z * value[j].z + value[j].w * value[j].w);
+      }
+      const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)vdim + eps);
+#pragma unroll
+      for (int j = 0; j < kHeadPieces; ++j) {
+        const int at = lane + 32 * j;
+        if (at < pieces) {
+          const float4 scale = reinterpret_cast<const float4*>(w)[at];
+          const float v4[4] = {value[j].x * inv * scale.x, value[j].y * inv * scale.y, value[j].z * inv * scale.z, value[j].w * inv * scale.w};
+          Four<T> o;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float gv = to_float(g[j].v[e]);
+            o.v[e] = from_float<T>(v4[e] * (activation ? gv * sigmoid_f(gv) : sigmoid_f(gv)));
+          }
+          reinterpret_cast<Four<T>*>(dst)[at] = o;
+        }
+      }
+      continue;
     }
-#pragma unroll
-    for (int j = 0; j < kHeadPieces; ++j) {
-      value[j].x /= divisor, value[j].y /= divisor, value[j].z /= divisor, value[j].w /= divisor;
-      sum_sq += (value[j].x * value[j].x + value[j].y * value[j].y) + (value[j].z * value[j].z + value[j].w * value[j].w);
+    float sum_sq = 0.f;
+    for (int c = lane; c < vdim; c += 32) {
+      const float value = row[c] / divisor;
+      sum_sq += value * value;
     }
     const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)vdim + eps);
-#pragma unroll
-    for (int j = 0; j < kHeadPieces; ++j) {
-      const int at = lane + 32 * j;
-      if (at < pieces) {
-        const float4 scale = reinterpret_cast<const float4*>(w)[at];
-        const float v4[4] = {value[j].x * inv * scale.x, value[j].y * inv * scale.y, value[j].z * inv * scale.z, value[j].w * inv * scale.w};
-        Four<T> o;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float gv = to_float(g[j].v[e]);
-          o.v[e] = from_float<T>(v4[e] * (activation ? gv * sigmoid_f(gv) : sigmoid_f(gv)));
-        }
-        reinterpret_cast<Four<T>*>(dst)[at] = o;
-      }
+    for (int c = lane; c < vdim; c += 32) {
+      const float g = to_float(z[c]);
+      const float factor = activation ? g * sigmoid_f(g) : sigmoid_f(g);
+      dst[c] = from_float<T>((row[c] / divisor) * inv * w[c] * factor);
     }
-    return;
-  }
-  float sum_sq = 0.f;
-  for (int c = lane; c < vdim; c += 32) {
-    const float value = row[c] / divisor;
-    sum_sq += value * value;
-  }
-  const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)vdim + eps);
-  for (int c = lane; c < vdim; c += 32) {
-    const float g = to_float(z[c]);
-    const float factor = activation ? g * sigmoid_f(g) : sigmoid_f(g);
-    dst[c] = from_float<T>((row[c] / divisor) * inv * w[c] * factor);
   }
 }
 
@@ -564,9 +565,10 @@ MS_EXPORT int ms_head_norm_gate(const float* y, const float* bottom, const float
                                 int heads, int vdim, cudaStream_t stream) {
   if (n_tokens == 0 || heads == 0 || vdim == 0) return 0;
   MS_REQUIRE(activation == 0 || activation == 1, "head_norm_gate: activation code %d", activation);
-  const int warps = 4;
-  const long long blocks = ((long long)n_tokens * heads + warps - 1) / warps;
-  MS_REQUIRE(blocks < 2147483647LL, "head_norm_gate: %lld heads in one launch is too many", (long long)n_tokens * heads);
+  // blocks of eight warps that walk the (token, head) pairs with the grid's stride: at most sixteen blocks a multiprocessor
+  const int warps = 8;
+  long long blocks = ((long long)n_tokens * heads + warps - 1) / warps;
+  if (blocks > 16LL * scan_sm_count()) blocks = 16LL * scan_sm_count();
   const size_t element = dtype == MS_F32 ? 4 : 2;
   const int wide = vdim % 4 == 0 && vdim <= 128 * kHeadPieces && gate_ld % 4 == 0 && gate_col % 4 == 0 &&
                    reinterpret_cast<size_t>(y) % 16 == 0 && reinterpret_cast<size_t>(weight) % 16 == 0 &&
