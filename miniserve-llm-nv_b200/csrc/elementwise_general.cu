@@ -289,6 +289,34 @@ __global__ void silu_mul_bias_kernel(const T* __restrict__ gate_up, const float*
   out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
+// The same, four numbers a thread in 16-byte (8-byte for bfloat16) accesses, where `inter` is a multiple of four and
+// the arrays lie on such boundaries.
+template <typename T> struct alignas(sizeof(T) * 4) Quad { T v[4]; };
+
+template <typename T>
+__global__ void silu_mul_bias_quad_kernel(const T* __restrict__ gate_up, const float* __restrict__ bias, T* __restrict__ out,
+                                          size_t quads, int inter) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= quads) return;
+  const int per_row = inter >> 2;
+  const size_t n = i / per_row;
+  const int c = (int)(i % per_row) * 4;
+  const Quad<T> gate = *reinterpret_cast<const Quad<T>*>(gate_up + n * 2 * inter + c);
+  const Quad<T> up = *reinterpret_cast<const Quad<T>*>(gate_up + n * 2 * inter + inter + c);
+  const float4 gate_bias = *reinterpret_cast<const float4*>(bias + c), up_bias = *reinterpret_cast<const float4*>(bias + inter + c);
+  const float gb[4] = {gate_bias.x, gate_bias.y, gate_bias.z, gate_bias.w}, ub[4] = {up_bias.x, up_bias.y, up_bias.z, up_bias.w};
+  Quad<T> result;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float g = to_float(gate.v[e]) + gb[e];
+    const float u = to_float(up.v[e]) + ub[e];
+    result.v[e] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+  *reinterpret_cast<Quad<T>*>(out + i * 4) = result;
+}
+
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, size_t total, int width) {
   grid_dependency_wait();
@@ -315,6 +343,16 @@ MS_EXPORT int ms_silu_mul_bias(const void* gate_up, int dtype, const float* bias
                                cudaStream_t stream) {
   const long long total = (long long)n_tokens * inter;
   if (total == 0) return 0;
+  const size_t four = dtype == MS_F32 ? 16 : 8;
+  if (inter % 4 == 0 && reinterpret_cast<size_t>(gate_up) % four == 0 && reinterpret_cast<size_t>(out) % four == 0 &&
+      reinterpret_cast<size_t>(bias) % 16 == 0) {
+    const long long quads = total / 4, quad_blocks = (quads + 255) / 256;
+    MS_REQUIRE(quad_blocks < 2147483647LL, "silu_mul_bias: %lld elements in one launch is too many", total);
+    MS_EG_DISPATCH(dtype, (ms::launch(silu_mul_bias_quad_kernel<T>, (unsigned)quad_blocks, 256, 0, stream, (const T*)gate_up, bias,
+                                      (T*)out, (size_t)quads, inter)));
+    MS_CHECK_LAUNCH("silu_mul_bias");
+    return 0;
+  }
   const long long blocks = (total + 255) / 256;
   MS_REQUIRE(blocks < 2147483647LL, "silu_mul_bias: %lld elements in one launch is too many", total);
   MS_EG_DISPATCH(dtype, (ms::launch(silu_mul_bias_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)gate_up, bias, (T*)out,
