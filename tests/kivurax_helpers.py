@@ -70,7 +70,7 @@ KIVURAX_C = dict(architecture="Kivurax", vocab=300, width=128, norm=dict(eps=1e-
     layer(mlstm(2, 128, 64, 15.0), dense(256)),
     layer(side(8, 1, 64, 0.125, 40, rot(1000000.0, 64, (8.0, 128, 32.0, 1.0)), 256, 8, 4, 1.0, 1.0), moe(16, 4, 32)),
     layer(delta(4, 2, 64, 32, 4), moe(12, 2, 32)),
-    layer(side(4, 2, 128, 0.09, 100, rot(10000.0, 64), 128, 2, 4, 1.2, 0.9), dense(128)),
+    layer(side(4, 2, 128, 0.09, 100, rot(10000.0, 64), 128, 2, 4, 1.1, 0.7), dense(128)),
     layer(delta(2, 1, 256, 16, 3), moe(16, 4, 32)),
     layer(mlstm(4, 64, 128, 15.0), moe(12, 2, 32)),
 ])

@@ -380,7 +380,7 @@ def with_rounded_projections(run, wd, p, names, width):
 def in_portions(part, views_of, harness, dtype, first, second, third, run_plain, cuts=None):
     """Feeds ``first`` in portions (down to one and two tokens) and then token by token beside ``second`` in the same steps,
     then ``third`` in the slot that the first request gave back; everything against ``run_plain`` of each sequence alone."""
-    cuts = cuts or [0, 1, 3, 5, 70, 72, 150] + list(range(151, len(first) + 1))
+    cuts = cuts or [0, 1, 3, 5, 62, 64, 150] + list(range(151, len(first) + 1))
     got_first, got_second, at = [], [], 0
     for start, end in zip(cuts[:-1], cuts[1:]):
         portions = {"a": end - start}
