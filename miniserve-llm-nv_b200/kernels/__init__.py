@@ -749,7 +749,7 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col: int, weight: to
 
 # --------------------------------------------------------------------------- recurrences that carry a matrix or a vector
 
-MAX_MATRIX_SCAN_DIM = 512     # entries of a query or key that matrix_scan spreads over a warp (32 lanes x 16)
+MAX_MATRIX_SCAN_DIM = 512     # entries of a query or key that matrix_scan spreads over a column's lanes (16 lanes x 32)
 MATRIX_SCAN_MODES = {"memory": 0, "delta": 1}
 HEAD_GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
 
