@@ -74,7 +74,20 @@ KIVURAX_C = dict(architecture="Kivurax", vocab=300, width=128, norm=dict(eps=1e-
     layer(delta(2, 1, 256, 16, 3), moe(16, 4, 32)),
     layer(mlstm(4, 64, 128, 15.0), moe(12, 2, 32)),
 ])
-CONFIGS = {"a": KIVURAX_A, "b": KIVURAX_B, "c": KIVURAX_C}
+# No attention at all (no pages are needed, only state slots), a layer list that ends without a feed-forward.
+KIVURAX_D = dict(architecture="Kivurax", vocab=190, width=64, norm=dict(eps=1e-5), residual_mult=0.8, layers=[
+    layer(delta(4, 1, 16, 24, 3), dense(48)),
+    layer(mlstm(2, 32, 16, 8.0), moe(4, 2, 20)),
+    layer(mlstm(4, 12, 20, 20.0), dense(32)),
+    layer(delta(2, 2, 24, 32, 4), None),
+])
+# Nothing but side-by-side layers: heads of 32 and of 16 over one key head, a window shorter than a page and one that no
+# request of the tests outgrows.
+KIVURAX_E = dict(architecture="Kivurax", vocab=120, width=48, norm=dict(eps=1e-6), residual_mult=0.6, layers=[
+    layer(side(3, 3, 32, 0.2, 9, rot(2000.0, 32, (3.0, 32, 16.0, 1.0)), 40, 4, 3, 0.9, 1.1), moe(5, 2, 16)),
+    layer(side(4, 1, 16, 0.3, 500, rot(700.0, 8), 24, 3, 2, 1.4, 0.6), dense(36)),
+])
+CONFIGS = {"a": KIVURAX_A, "b": KIVURAX_B, "c": KIVURAX_C, "d": KIVURAX_D, "e": KIVURAX_E}
 
 
 def _normal(shape, seed, std, mean=0.0):

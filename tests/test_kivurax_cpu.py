@@ -167,7 +167,7 @@ def cpu_runtime(monkeypatch, tmp_path):
     return build
 
 
-@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 4)])
+@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 4), ("d", 8), ("e", 16)])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_cuttings_match_plain_on_cpu(cpu_runtime, name, page_size, cutting):
     from miniserve_b200.trace import TraceSession

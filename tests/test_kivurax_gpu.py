@@ -461,6 +461,8 @@ WINDOW_ALONE = [
     (96, dict(heads=4, kv_heads=2, dim=128, vdim=128, scale=0.09, mask=dict(size=100), rot=kh.rot(10000.0, 64))),
     (80, dict(heads=5, kv_heads=5, dim=6, vdim=6, scale=0.6, mask=dict(size=7), rot=kh.rot(20000.0, 2))),
     (64, dict(heads=4, kv_heads=4, dim=48, vdim=48, scale=0.14, mask=dict(size=400), rot=kh.rot(300.0, 48, (2.0, 32, 4.0, 1.0)))),
+    (64, dict(heads=4, kv_heads=2, dim=32, vdim=32, scale=0.18, mask=dict(size=33), rot=kh.rot(10000.0, 32))),
+    (96, dict(heads=2, kv_heads=1, dim=96, vdim=96, scale=0.1, mask=dict(size=50), rot=kh.rot(500000.0, 64, (4.0, 256, 16.0, 2.0)))),
 ]
 SIDE_RIGHT = dict(width=24, blocks=2, conv=3)
 
@@ -650,7 +652,7 @@ LENGTHS = (1, 7, 8, 9, 16, 17, 33, 64, 65, 150, 301)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 16), ("c", 16), ("b", 4), ("c", 64)])
+@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 16), ("c", 16), ("b", 4), ("c", 64), ("d", 8), ("e", 16)])
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
 def test_cuttings_against_plain(tmp_path, request, dtype, name, page_size, cutting):
     """Whole prompts; last tokens decoded one by one (windows pass over decoded tokens); portions down to two tokens; unequal
