@@ -463,6 +463,7 @@ WINDOW_ALONE = [
     (64, dict(heads=4, kv_heads=4, dim=48, vdim=48, scale=0.14, mask=dict(size=400), rot=kh.rot(300.0, 48, (2.0, 32, 4.0, 1.0)))),
     (64, dict(heads=4, kv_heads=2, dim=32, vdim=32, scale=0.18, mask=dict(size=33), rot=kh.rot(10000.0, 32))),
     (96, dict(heads=2, kv_heads=1, dim=96, vdim=96, scale=0.1, mask=dict(size=50), rot=kh.rot(500000.0, 64, (4.0, 256, 16.0, 2.0)))),
+    (72, dict(heads=6, kv_heads=2, dim=64, vdim=64, scale=0.12, mask=dict(size=30), rot=kh.rot(40000.0, 32))),
 ]
 SIDE_RIGHT = dict(width=24, blocks=2, conv=3)
 
