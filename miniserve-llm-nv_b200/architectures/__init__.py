@@ -1,3 +1,3 @@
 """Architectures known to the registry; importing this package registers them."""
 
-from . import kivurax, qwen3, vesidra, zozezen  # noqa: F401
+from . import bafavik, kivurax, qwen3, vesidra, zozezen  # noqa: F401

@@ -108,7 +108,7 @@ class CacheManager:
         self.requests: dict[str, RequestCache] = {}
         self._next_step = 0
         self._open: Optional[StepReservation] = None
-        shareable = all(need.window is None for need in self.paged_needs) and not self.state_needs and self.paged_needs
+        shareable = all(need.keeps_all for need in self.paged_needs) and not self.state_needs and self.paged_needs
         self.prefix: Optional[PrefixCache] = (
             PrefixCache(prefix_namespace, page_size, prefix_cache_max_entries)
             if enable_prefix_cache and shareable else None)
@@ -181,7 +181,7 @@ class CacheManager:
         entry = self.requests[request_id]
         if not 0 <= length <= entry.length:
             raise ValueError(f"request {request_id!r} holds {entry.length} tokens; cannot truncate to {length}")
-        if any(need.window is not None for need in self.paged_needs) or self.state_needs:
+        if any(not need.keeps_all for need in self.paged_needs) or self.state_needs:
             raise RuntimeError("truncate needs every token's keys and no per-request state")
         keep = (length + self.page_size - 1) // self.page_size
         if length % self.page_size:
@@ -317,10 +317,10 @@ class CacheManager:
             entry.tables = [list(table) for table in item.tables]
             entry.length = item.end
             for group, need in enumerate(self.paged_needs):
-                if need.window is None:
+                if need.keeps_all:
                     continue
-                # the next query sits at position `length`; it sees keys from length - window + 1 on
-                first_needed = entry.length - need.window + 1
+                # the next query sits at position `length`; it sees keys from length - window + 1 on (or from its chunk's start)
+                first_needed = need.first_needed(entry.length)
                 table = entry.tables[group]
                 for index in range(len(table)):
                     if (index + 1) * self.page_size > first_needed:

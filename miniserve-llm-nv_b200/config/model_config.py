@@ -686,3 +686,266 @@ class KivuraxConfig:
                   for layer in self.layers]
         return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, norm=dict(eps=self.eps),
                     residual_mult=self.residual_mult, layers=layers)
+
+
+# --------------------------------------------------------------------------- Bafavik
+
+
+def _rotation_or_none(data: Mapping[str, Any], where: str) -> RotationConfig:
+    rot = _section(data, "rot", where)
+    if _count(rot, "dims", 0) == 0:
+        return RotationConfig(base=_positive(rot, "base", where + "rot."), dims=0)
+    return RotationConfig.from_dict(rot, where + "rot.")
+
+
+@dataclass(frozen=True)
+class RotaryAttentionConfig:
+    """Grouped-query softmax attention with a rotation of the first ``rot.dims`` entries of a head, values of their own size
+    and, where ``conv`` is given, a short causal convolution of that many taps on queries, keys and values."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: RotationConfig
+    conv: Any = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str, conv: bool = False) -> "RotaryAttentionConfig":
+        config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
+                     vdim=_integer(data, "vdim"), scale=_positive(data, "scale", where), rot=_rotation_or_none(data, where),
+                     conv=_integer(data, "conv") if conv else None)
+        if config.heads % config.kv_heads:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")
+        if config.rot.dims > config.dim:
+            raise ValueError(f"{where}rot.dims {config.rot.dims} exceeds the head size dim {config.dim}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        out = dict(heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim, scale=self.scale,
+                   rot=dict(base=self.rot.base, dims=self.rot.dims))
+        if self.conv is not None:
+            out["conv"] = self.conv
+        return out
+
+
+@dataclass(frozen=True)
+class LinearAttentionConfig:
+    """Linear attention with a constant decay per head (``decay``: one number per head)."""
+
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "LinearAttentionConfig":
+        decay = data.get("decay")
+        if not isinstance(decay, (list, tuple)) or not all(isinstance(v, (int, float)) and not isinstance(v, bool) for v in decay):
+            raise ValueError(f"{where}decay must be a list of numbers, got {decay!r}")
+        config = cls(heads=_integer(data, "heads"), dim=_integer(data, "dim"), vdim=_integer(data, "vdim"),
+                     decay=tuple(float(v) for v in decay))
+        if len(config.decay) != config.heads or not all(math.isfinite(v) for v in config.decay):
+            raise ValueError(f"{where}decay must hold one finite number for each of the {config.heads} heads")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(heads=self.heads, dim=self.dim, vdim=self.vdim, decay=list(self.decay))
+
+
+@dataclass(frozen=True)
+class ChannelDeltaRuleConfig:
+    """The gated delta rule with a decay per head and key channel; the decay's and the output gate's projections are products
+    of two matrices through ``decay_rank`` and ``gate_rank`` numbers, which a checkpoint's tensor shapes give where
+    ``config.json`` does not."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: Any = None
+    gate_rank: Any = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "ChannelDeltaRuleConfig":
+        config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
+                     vdim=_integer(data, "vdim"), conv=_integer(data, "conv"),
+                     decay_rank=_integer(data, "decay_rank") if "decay_rank" in data else None,
+                     gate_rank=_integer(data, "gate_rank") if "gate_rank" in data else None)
+        if config.heads % config.kv_heads:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        out = dict(heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim, conv=self.conv)
+        for key in ("decay_rank", "gate_rank"):
+            if getattr(self, key) is not None:
+                out[key] = getattr(self, key)
+        return out
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionConfig:
+    """Differential attention without rotation under a chunked mask of ``chunk`` positions."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    diff: float
+    chunk: int
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "DifferentialAttentionConfig":
+        config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
+                     vdim=_integer(data, "vdim"), scale=_positive(data, "scale", where), diff=_number(data, "diff"),
+                     chunk=_integer(_section(data, "mask", where), "size"))
+        if config.heads % config.kv_heads:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")
+        if not math.isfinite(config.diff):
+            raise ValueError(f"{where}diff must be finite, got {config.diff}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim, scale=self.scale, diff=self.diff,
+                    mask=dict(size=self.chunk))
+
+
+@dataclass(frozen=True)
+class BafavikPairConfig:
+    """Two mixers that read the same input.  ``parallel``: rotary attention beside linear attention, summed with a scale each.
+    ``parallel_2``: convolved rotary attention beside the channel delta rule, each output normed, half their sum."""
+
+    left: Any
+    right: Any
+    left_scale: Any = None
+    right_scale: Any = None
+
+    @classmethod
+    def scaled(cls, data: Mapping[str, Any], where: str) -> "BafavikPairConfig":
+        return cls(left=RotaryAttentionConfig.from_dict(_section(data, "left", where), where + "left."),
+                   right=LinearAttentionConfig.from_dict(_section(data, "right", where), where + "right."),
+                   left_scale=_number(data, "left_scale"), right_scale=_number(data, "right_scale"))
+
+    @classmethod
+    def normed(cls, data: Mapping[str, Any], where: str) -> "BafavikPairConfig":
+        return cls(left=RotaryAttentionConfig.from_dict(_section(data, "left", where), where + "left.", conv=True),
+                   right=ChannelDeltaRuleConfig.from_dict(_section(data, "right", where), where + "right."))
+
+    def to_dict(self) -> dict[str, Any]:
+        out = dict(left=self.left.to_dict(), right=self.right.to_dict())
+        if self.left_scale is not None:
+            out.update(left_scale=self.left_scale, right_scale=self.right_scale)
+        return out
+
+
+@dataclass(frozen=True)
+class BafavikLayerConfig:
+    type: str       # "parallel", "attention" or "parallel_2"
+    mixer: Any
+    ff: Any         # inner size of the dense feed-forward, or None
+
+
+@dataclass(frozen=True)
+class TokenPairConfig:
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
+class BafavikConfig:
+    """The Bafavik decoder: ``config.json`` holds ``architecture``, ``vocab``, ``width``, ``norm.eps``, ``residual_mult``,
+    ``logit_scale``, ``embedding`` (``scale`` and, optionally, ``bigram`` with ``buckets``, ``mul_prev``, ``mul_cur``), ``loop``
+    (``start``, ``stop``, ``times``: those layers run that often in a row, or null) and ``layers``, a list whose entries give each
+    layer's mixer ``type`` (``parallel``, ``attention`` or ``parallel_2``), the mixer's sizes and constants (``mixer``) and its
+    feed-forward (``mlp`` with ``kind`` "dense" and ``ff``, or null).  Every size and constant is read."""
+
+    vocab: int
+    width: int
+    eps: float
+    residual_mult: float
+    logit_scale: float
+    embedding_scale: float
+    bigram: Any
+    loop: Any       # None or (start, stop, times)
+    layers: tuple
+    architecture: str = "Bafavik"
+
+    MIXERS = {"parallel": BafavikPairConfig.scaled, "attention": DifferentialAttentionConfig.from_dict,
+              "parallel_2": BafavikPairConfig.normed}
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "BafavikConfig":
+        if data.get("architecture") != "Bafavik":
+            raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: expected architecture 'Bafavik', got {data.get('architecture')!r}")
+        raw_layers = data.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ValueError("layers must be a non-empty list in the model config")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"layers[{index}]."
+            if not isinstance(raw, Mapping):
+                raise ValueError(f"layers[{index}] must be an object")
+            kind = raw.get("type")
+            if kind not in cls.MIXERS:
+                raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}type {kind!r} is not implemented "
+                                            f"({', '.join(cls.MIXERS)})")
+            mixer = cls.MIXERS[kind](_section(raw, "mixer", where), where + "mixer.")
+            ff = None
+            if raw.get("mlp") is not None:
+                mlp = _section(raw, "mlp", where)
+                if mlp.get("kind") != "dense":
+                    raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}mlp.kind {mlp.get('kind')!r} is not implemented (dense)")
+                ff = _integer(mlp, "ff")
+            layers.append(BafavikLayerConfig(kind, mixer, ff))
+        embedding = _section(data, "embedding", "")
+        bigram = None
+        if embedding.get("bigram") is not None:
+            raw = _section(embedding, "bigram", "embedding.")
+            bigram = TokenPairConfig(_integer(raw, "buckets"), _count(raw, "mul_prev", 0), _count(raw, "mul_cur", 0))
+        loop = None
+        if data.get("loop") is not None:
+            raw = _section(data, "loop", "")
+            loop = (_count(raw, "start", 0), _integer(raw, "stop"), _integer(raw, "times"))
+            if not loop[0] < loop[1] <= len(layers):
+                raise ValueError(f"loop: layers {loop[0]} .. {loop[1]} - 1 are not a run of the model's {len(layers)} layers")
+        mult, logit_scale = _number(data, "residual_mult"), _number(data, "logit_scale")
+        if not math.isfinite(mult) or not math.isfinite(logit_scale):
+            raise ValueError(f"residual_mult and logit_scale must be finite, got {mult} and {logit_scale}")
+        return cls(vocab=_integer(data, "vocab"), width=_integer(data, "width"),
+                   eps=_positive(_section(data, "norm", ""), "eps", "norm."), residual_mult=mult, logit_scale=logit_scale,
+                   embedding_scale=_number(embedding, "scale"), bigram=bigram, loop=loop, layers=tuple(layers))
+
+    def with_stored_shapes(self, shapes: Mapping[str, tuple]) -> "BafavikConfig":
+        """The configuration with the sizes that only a checkpoint's tensor shapes give: the inner sizes of the two-step
+        projections of the delta rule (the rows of ``l<i>.mix.right.a1`` and ``l<i>.mix.right.g1``)."""
+        from dataclasses import replace
+
+        layers = []
+        for index, layer in enumerate(self.layers):
+            if layer.type == "parallel_2":
+                right = layer.mixer.right
+                found = {}
+                for key, name in (("decay_rank", "a1"), ("gate_rank", "g1")):
+                    stored = shapes.get(f"l{index}.mix.right.{name}")
+                    if getattr(right, key) is None and stored is not None and len(stored) == 2:
+                        found[key] = int(stored[0])
+                if found:
+                    layer = replace(layer, mixer=replace(layer.mixer, right=replace(right, **found)))
+            layers.append(layer)
+        return replace(self, layers=tuple(layers))
+
+    def to_dict(self) -> dict[str, Any]:
+        """The ``config.json`` content that reads back as this configuration."""
+        layers = [dict(type=layer.type, mixer=layer.mixer.to_dict(), mlp=None if layer.ff is None else dict(kind="dense", ff=layer.ff))
+                  for layer in self.layers]
+        embedding: dict[str, Any] = dict(scale=self.embedding_scale)
+        if self.bigram is not None:
+            embedding["bigram"] = dict(buckets=self.bigram.buckets, mul_prev=self.bigram.mul_prev, mul_cur=self.bigram.mul_cur)
+        loop = None if self.loop is None else dict(start=self.loop[0], stop=self.loop[1], times=self.loop[2])
+        return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, norm=dict(eps=self.eps),
+                    residual_mult=self.residual_mult, logit_scale=self.logit_scale, embedding=embedding, loop=loop, layers=layers)

@@ -78,7 +78,14 @@ def read_config_json(folder: str | Path) -> dict[str, Any]:
 
 
 def load_model_config(folder: str | Path):
-    """``(architecture, typed configuration)`` of a model folder."""
+    """``(architecture, typed configuration)`` of a model folder.  A configuration class that offers
+    ``with_stored_shapes(shapes)`` is also shown the shapes of the folder's tensors: some designs leave sizes out of
+    ``config.json`` that the checkpoint alone gives."""
     data = read_config_json(folder)
     architecture = resolve_architecture(data)
-    return architecture, architecture.config_class.from_dict(data)
+    config = architecture.config_class.from_dict(data)
+    if hasattr(config, "with_stored_shapes"):
+        from ..weights.loader import stored_shapes
+
+        config = config.with_stored_shapes(stored_shapes(folder))
+    return architecture, config

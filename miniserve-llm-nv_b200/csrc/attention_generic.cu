@@ -71,7 +71,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                const int* __restrict__ positions, int page_size, int n_q, int n_kv,
                                                int d, float scale, int window, float softcap,
                                                const float* __restrict__ bias_slopes, T* __restrict__ out, int dv,
-                                               int sink, const T* __restrict__ gate, int gate_ld) {
+                                               int sink, const T* __restrict__ gate, int gate_ld, int chunk) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float smem[];
@@ -90,7 +90,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
   __syncthreads();
 
   const float slope = bias_slopes ? bias_slopes[head] : 0.f;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) first_key = max(first_key, pos - pos % chunk);     // chunks are counted from position 0 of the sequence
   const int last_key = pos;  // inclusive
   float m = -INFINITY, l = 0.f;
   float acc[kMaxLanesPerThread];
@@ -168,12 +169,13 @@ using namespace ms;
 // (window <= 0: no window); they must already be in the pool.  softcap <= 0: no soft cap; bias_slopes
 // [n_q] float32 or null.  dv: the size of a value head (value pool [pages, n_kv, page_size, dv], out [n_tokens, n_q, dv]);
 // sink != 0: one more term exp(0) in the softmax's denominator; gate (null: none): logits of the model's element type,
-// gate[token * gate_ld + head], whose sigmoid multiplies the head's output.
+// gate[token * gate_ld + head], whose sigmoid multiplies the head's output.  chunk > 0: a token sees only the keys of its own
+// chunk of `chunk` positions (position p: keys p - p % chunk .. p).
 MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k_pool, const void* v_pool,
                                          const int* block_tables, int table_stride, const int* request_of_token,
                                          const int* positions, int page_size, int n_q, int n_kv, int d, float scale,
                                          int window, float softcap, const float* bias_slopes, void* out, int n_tokens,
-                                         int dv, int sink, const void* gate, int gate_ld, cudaStream_t stream) {
+                                         int dv, int sink, const void* gate, int gate_ld, int chunk, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(d > 0 && d <= 32 * kMaxLanesPerThread, "paged_attention: head size %d outside 1..%d", d,
              32 * kMaxLanesPerThread);
@@ -189,12 +191,12 @@ MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k
     ms::launch(paged_attention_generic_kernel<float>, grid, kAttnWarps * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, table_stride, request_of_token,
         positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes, (float*)out, dv, sink,
-        (const float*)gate, gate_ld);
+        (const float*)gate, gate_ld, chunk);
   } else if (dtype == MS_BF16) {
     ms::launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, kAttnWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_tables,
         table_stride, request_of_token, positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes,
-        (__nv_bfloat16*)out, dv, sink, (const __nv_bfloat16*)gate, gate_ld);
+        (__nv_bfloat16*)out, dv, sink, (const __nv_bfloat16*)gate, gate_ld, chunk);
   } else {
     MS_FAIL("paged_attention: unknown element type code %d", dtype);
   }

@@ -22,7 +22,7 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
                          int n_kv, int d, int dv, float scale_log2, int window, __nv_bfloat16* __restrict__ out,
                          float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits, int sink,
-                         const __nv_bfloat16* __restrict__ gate, int gate_ld) {
+                         const __nv_bfloat16* __restrict__ gate, int gate_ld, int chunk) {
   grid_dependency_wait();
   grid_dependency_launch();
   constexpr int BM = 16 * W, THREADS = 32 * W;
@@ -50,6 +50,7 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int t_hi = last_row / group;
   int key_begin = 0;
   if (window > 0) key_begin = max(0, first_pos + t_lo - window + 1);
+  if (chunk > 0) key_begin = max(key_begin, (first_pos + t_lo) - (first_pos + t_lo) % chunk);      // the lowest row's chunk
   const int key_end = first_pos + t_hi + 1;
   const int tile_begin = (key_begin / BN) * BN;
   const int n_tiles = (key_end - tile_begin + BN - 1) / BN;
@@ -166,7 +167,7 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + n * 8 + quad_col * 2 + (e & 1);
         const int p = pos[e >> 1];
-        const bool visible = key <= p && (window <= 0 || key > p - window);
+        const bool visible = key <= p && (window <= 0 || key > p - window) && (chunk <= 0 || key >= p - p % chunk);
         if (!visible) acc_s[n][e] = -INFINITY;
         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], acc_s[n][e]);
       }
@@ -280,7 +281,7 @@ int launch_attention_any(const void* q, const void* k_pool, const void* v_pool, 
                          const int* query_start, const int* context_lens, int page_size, int n_q, int n_kv, int d, int dv,
                          float scale, int window, void* out, float* part_o, float* part_lse, int num_splits, int n_requests,
                          int max_query_len, int n_tokens, int sink, const void* gate, int gate_ld, int first_token,
-                         cudaStream_t stream) {
+                         int chunk, cudaStream_t stream) {
   constexpr int BM = 16 * W;
   const size_t smem = (size_t)(BM * (d + 8) + 2 * BN * (d + 8) + 2 * BN * (dv + 8)) * sizeof(__nv_bfloat16) + 2 * BN * sizeof(long long);
   auto kernel = attention_mma_any_kernel<W, BN>;
@@ -298,7 +299,7 @@ int launch_attention_any(const void* q, const void* k_pool, const void* v_pool, 
   dim3 grid((unsigned)tiles, n_kv, n_requests * num_splits);
   ms::launch(kernel, grid, W * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
              block_tables, table_stride, query_start, context_lens, page_size, n_q, n_kv, d, dv, scale * 1.4426950408889634f, window,
-             (__nv_bfloat16*)out, part_o, part_lse, num_splits, sink, (const __nv_bfloat16*)gate, gate_ld);
+             (__nv_bfloat16*)out, part_o, part_lse, num_splits, sink, (const __nv_bfloat16*)gate, gate_ld, chunk);
   MS_CHECK_LAUNCH("attention_mma_any");
   if (num_splits > 1) {
     const size_t skip = (size_t)first_token * n_q;
@@ -340,7 +341,7 @@ MS_EXPORT int ms_paged_attention_mma_any(const void* q, const void* k_pool, cons
                                          int table_stride, const int* query_start, const int* context_lens, int page_size,
                                          int n_q, int n_kv, int d, int dv, float scale, int window, void* out, float* part_o,
                                          float* part_lse, int num_splits, int n_requests, int max_query_len, int n_tokens,
-                                         int sink, const void* gate, int gate_ld, int first_token, cudaStream_t stream) {
+                                         int sink, const void* gate, int gate_ld, int first_token, int chunk, cudaStream_t stream) {
   if (n_tokens == 0 || n_requests == 0) return 0;
   MS_REQUIRE(ms_attention_mma_any_supports(d, dv), "attention (any head size): sizes %d and %d are not multiples of 16 up to %d", d, dv, kAnyMax);
   MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d query heads are not a multiple of %d key/value heads", n_q, n_kv);
@@ -351,8 +352,8 @@ MS_EXPORT int ms_paged_attention_mma_any(const void* q, const void* k_pool, cons
   if (small)
     return launch_attention_any<1, 32>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens, page_size, n_q, n_kv, d,
                                        dv, scale, window, out, part_o, part_lse, num_splits, n_requests, max_query_len, n_tokens, sink,
-                                       gate, gate_ld, first_token, stream);
+                                       gate, gate_ld, first_token, chunk, stream);
   return launch_attention_any<4, 64>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens, page_size, n_q, n_kv, d, dv,
                                      scale, window, out, part_o, part_lse, num_splits, n_requests, max_query_len, n_tokens, sink, gate,
-                                     gate_ld, first_token, stream);
+                                     gate_ld, first_token, chunk, stream);
 }

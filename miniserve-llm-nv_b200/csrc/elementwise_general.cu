@@ -15,7 +15,8 @@
 namespace ms {
 
 // For output row k (source row r = rows ? rows[k] : k):
-//   a = post_scale * post_weight * delta[r] / sqrt(mean(delta[r]^2) + post_eps)      (delta null: a = 0)
+//   a = post_scale * post_weight * delta[r] / sqrt(mean(delta[r]^2) + post_eps)      (delta null: a = 0;
+//       post_eps < 0: no division, a = post_scale * post_weight * delta[r], a scale per channel)
 //   x = residual[r] + a            (float32; written back to residual unless rows are gathered)
 //   out[k] = weight * x / sqrt(mean(x^2) + eps)     rounded once to T      (weight null: out[k] = x)
 // The row (width <= blockDim.x * kPostNormPerThread) stays in registers between the passes.
@@ -42,7 +43,7 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ residual, const 
     sum_sq += v[i] * v[i];
   }
   float inv_delta = 0.f;
-  if (delta) inv_delta = post_scale / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
+  if (delta) inv_delta = post_eps < 0.f ? post_scale : post_scale / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
   sum_sq = 0.f;
 #pragma unroll
   for (int i = 0; i < kPostNormPerThread; ++i) {
@@ -96,7 +97,7 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, co
     }
   }
   float inv_delta = 0.f;
-  if (delta) inv_delta = post_scale / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
+  if (delta) inv_delta = post_eps < 0.f ? post_scale : post_scale / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
   sum_sq = 0.f;
 #pragma unroll
   for (int i = 0; i < CHUNKS; ++i) {
@@ -138,12 +139,15 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, co
 // Rotation: the first rotary_dim entries of a head, entry i paired with entry i + rotary_dim / 2 (interleaved: entry 2i with
 // entry 2i + 1); the pair (u, v)
 // becomes (u cos - v sin, v cos + u sin) with (cos, sin) = cos_sin[n, i].  A negative slot skips the writes.
+// bias (null: none): float32 [ld], the projection's bias column by column, added in float32 to every head as it is read.
+// value_heads: the projection holds that many value heads (a divisor of n_kv); the pool's value head g is head g % value_heads.
 template <typename T>
 __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv,
                                    int d, int dv, const int* __restrict__ slots, const float* __restrict__ q_weight,
                                    const float* __restrict__ k_weight, float eps, const float2* __restrict__ cos_sin,
                                    int rotary_dim, T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
-                                   T* __restrict__ q_out, int n_tokens, int interleaved) {
+                                   T* __restrict__ q_out, int n_tokens, int interleaved, const float* __restrict__ bias,
+                                   int value_heads) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float prepare_smem[];
@@ -169,9 +173,14 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col
     const int page = slot / page_size, offset = slot % page_size;
     if (head >= n_q + n_kv) {
       const int g = head - n_q - n_kv;
-      src = row + v_col + g * dv;
+      src = row + v_col + (g % value_heads) * dv;        // (fewer projected value heads than key heads: they repeat)
       dst = v_pool + (((size_t)page * n_kv + g) * page_size + offset) * dv;
-      for (int c = lane; c < dv; c += 32) dst[c] = src[c];
+      if (bias) {
+        const float* b = bias + v_col + (g % value_heads) * dv;
+        for (int c = lane; c < dv; c += 32) dst[c] = from_float<T>(to_float(src[c]) + b[c]);
+      } else {
+        for (int c = lane; c < dv; c += 32) dst[c] = src[c];
+      }
       return;
     }
     const int g = head - n_q;
@@ -180,8 +189,9 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col
     weight = k_weight;
   }
   float sum_sq = 0.f;
+  const float* head_bias = bias ? bias + (src - row) : nullptr;      // (the projection's bias lies by its columns)
   for (int c = lane; c < d; c += 32) {
-    const float v = to_float(src[c]);
+    const float v = to_float(src[c]) + (head_bias ? head_bias[c] : 0.f);
     x[c] = v;
     sum_sq += v * v;
   }
@@ -253,13 +263,14 @@ MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dt
 MS_EXPORT int ms_qkv_prepare(const void* proj, int dtype, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv, int d,
                              int dv, const int* slots, const float* q_weight, const float* k_weight, float eps,
                              const float* cos_sin, int rotary_dim, void* k_pool, void* v_pool, int page_size, void* q_out,
-                             int n_tokens, int interleaved, cudaStream_t stream) {
+                             int n_tokens, int interleaved, const float* bias, int value_heads, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(d > 0 && d <= 1024 && dv > 0, "qkv_prepare: head sizes %d and %d", d, dv);
   MS_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
              "qkv_prepare: rotary size %d must be even and at most the head size %d", rotary_dim, d);
   MS_REQUIRE(page_size > 0, "qkv_prepare: page size must be positive, got %d", page_size);
   MS_REQUIRE(k_col < 0 || (v_col >= 0 && slots && k_pool && v_pool), "qkv_prepare: keys and values need their columns, slots and pools");
+  MS_REQUIRE(k_col < 0 || (value_heads >= 1 && n_kv % value_heads == 0), "qkv_prepare: %d value heads for %d key heads", value_heads, n_kv);
   const int warps = 4;
   const long long items = (long long)n_tokens * (n_q + (k_col >= 0 ? 2 * n_kv : 0));
   const long long blocks = (items + warps - 1) / warps;
@@ -267,7 +278,7 @@ MS_EXPORT int ms_qkv_prepare(const void* proj, int dtype, int ld, int q_col, int
   const size_t smem = (size_t)warps * d * sizeof(float);
   MS_EG_DISPATCH(dtype, (ms::launch(qkv_prepare_kernel<T>, (unsigned)blocks, warps * 32, smem, stream, (const T*)proj, ld, q_col,
                                     k_col, v_col, n_q, n_kv, d, dv, slots, q_weight, k_weight, eps, (const float2*)cos_sin,
-                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens, interleaved)));
+                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens, interleaved, bias, value_heads > 0 ? value_heads : 1)));
   MS_CHECK_LAUNCH("qkv_prepare");
   return 0;
 }
@@ -336,7 +347,112 @@ __global__ void scaled_sum_kernel(const T* __restrict__ a, float a_scale, const 
   out[i] = from_float<T>(a_scale * to_float(a[i]) + b_scale * to_float(b[i]));
 }
 
+// out[n] = a_scale * a_weight * a[n] / rms(a[n]) + b_scale * b_weight * b[n] / rms(b[n]): two outputs, each normed over the
+// row with a weight of its own, summed.  One block a row.
+template <typename T>
+__global__ void normed_sum_kernel(const T* __restrict__ a, const float* __restrict__ a_weight, float a_scale,
+                                  const T* __restrict__ b, const float* __restrict__ b_weight, float b_scale, float eps,
+                                  T* __restrict__ out, int hidden) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float scratch[32];
+  const T* ar = a + (size_t)blockIdx.x * hidden;
+  const T* br = b + (size_t)blockIdx.x * hidden;
+  float sa = 0.f, sb = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float x = to_float(ar[c]), y = to_float(br[c]);
+    sa += x * x;
+    sb += y * y;
+  }
+  const float inv_a = a_scale / sqrtf(block_sum(sa, scratch) / (float)hidden + eps);
+  const float inv_b = b_scale / sqrtf(block_sum(sb, scratch) / (float)hidden + eps);
+  T* dst = out + (size_t)blockIdx.x * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    dst[c] = from_float<T>(a_weight[c] * (to_float(ar[c]) * inv_a) + b_weight[c] * (to_float(br[c]) * inv_b));
+}
+
+// out[n, c] = x[n, c] * sigmoid(gate[n, gate_col + c]): a gate per entry on the concatenated heads.
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(const T* __restrict__ x, const T* __restrict__ gate, int gate_ld, int gate_col,
+                                        T* __restrict__ out, size_t total, int width) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float g = to_float(gate[(i / width) * gate_ld + gate_col + i % width]);
+  out[i] = from_float<T>(to_float(x[i]) / (1.f + expf(-g)));
+}
+
+// One warp per (token, head): o = first - lambda second with first = a[n, head], second = a[n, heads + head] (the outputs of
+// two score maps over the same values), o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate[n, gate_col + head dv + c]).
+template <typename T>
+__global__ void differential_combine_kernel(const T* __restrict__ a, int heads, int dv, float lambda, float eps,
+                                            float out_scale, const T* __restrict__ gate, int gate_ld, int gate_col,
+                                            T* __restrict__ out, long long items) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= items) return;
+  const size_t n = (size_t)(item / heads);
+  const int head = (int)(item % heads);
+  const T* first = a + (n * 2 * heads + head) * dv;
+  const T* second = a + (n * 2 * heads + heads + head) * dv;
+  float sum_sq = 0.f;
+  for (int c = lane; c < dv; c += 32) {
+    const float o = to_float(first[c]) - lambda * to_float(second[c]);
+    sum_sq += o * o;
+  }
+  const float inv = out_scale / sqrtf(warp_sum(sum_sq) / (float)dv + eps);
+  const T* g = gate ? gate + n * gate_ld + gate_col + (size_t)head * dv : nullptr;
+  T* dst = out + (n * heads + head) * dv;
+  for (int c = lane; c < dv; c += 32) {
+    float o = (to_float(first[c]) - lambda * to_float(second[c])) * inv;
+    if (g) o /= 1.f + expf(-to_float(g[c]));
+    dst[c] = from_float<T>(o);
+  }
+}
+
 }  // namespace ms
+
+// a, b, out [rows, hidden] of type `dtype`; the weights float32 [hidden].
+MS_EXPORT int ms_normed_sum(const void* a, const float* a_weight, float a_scale, const void* b, const float* b_weight,
+                            float b_scale, float eps, void* out, int dtype, int rows, int hidden, cudaStream_t stream) {
+  if (rows == 0 || hidden == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  MS_EG_DISPATCH(dtype, (ms::launch(normed_sum_kernel<T>, rows, threads, 0, stream, (const T*)a, a_weight, a_scale, (const T*)b,
+                                    b_weight, b_scale, eps, (T*)out, hidden)));
+  MS_CHECK_LAUNCH("normed_sum");
+  return 0;
+}
+
+// x, out [rows, width]; gate rows of gate_ld numbers, the logits from column gate_col; all of type `dtype` (out may be x).
+MS_EXPORT int ms_sigmoid_gate_mul(const void* x, const void* gate, int gate_ld, int gate_col, void* out, int dtype, int rows,
+                                  int width, cudaStream_t stream) {
+  const long long total = (long long)rows * width;
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "sigmoid_gate_mul: %lld elements in one launch is too many", total);
+  MS_EG_DISPATCH(dtype, (ms::launch(sigmoid_gate_mul_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)x, (const T*)gate, gate_ld,
+                                    gate_col, (T*)out, (size_t)total, width)));
+  MS_CHECK_LAUNCH("sigmoid_gate_mul");
+  return 0;
+}
+
+// a [tokens, 2 heads, dv] (the first map's heads, then the second's); gate rows of gate_ld numbers (null: no gate); out
+// [tokens, heads, dv]; all of type `dtype`.
+MS_EXPORT int ms_differential_combine(const void* a, int heads, int dv, float lambda, float eps, float out_scale,
+                                      const void* gate, int gate_ld, int gate_col, void* out, int dtype, int n_tokens,
+                                      cudaStream_t stream) {
+  const long long items = (long long)n_tokens * heads;
+  if (items == 0 || dv == 0) return 0;
+  const long long blocks = (items + 3) / 4;
+  MS_REQUIRE(blocks < 2147483647LL, "differential_combine: %lld heads in one launch is too many", items);
+  MS_EG_DISPATCH(dtype, (ms::launch(differential_combine_kernel<T>, (unsigned)blocks, 128, 0, stream, (const T*)a, heads, dv, lambda,
+                                    eps, out_scale, (const T*)gate, gate_ld, gate_col, (T*)out, items)));
+  MS_CHECK_LAUNCH("differential_combine");
+  return 0;
+}
 
 // gate_up [n_tokens, 2 inter] (gate columns, then up columns); bias float32 [2 inter]; out [n_tokens, inter].
 MS_EXPORT int ms_silu_mul_bias(const void* gate_up, int dtype, const float* bias, void* out, int n_tokens, int inter,

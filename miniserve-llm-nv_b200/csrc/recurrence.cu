@@ -8,6 +8,9 @@
 //   ms_matrix_scan            the recurrence over a dim x vdim matrix per head, in two forms:
 //                               memory: S = keep S + write k v^T, n = keep n + write k, y = S^T q, bottom = max(|n.q|, floor) + 1e-6
 //                               delta:  S = decay S, u = beta (v - S^T k), S = S + k u^T, y = S^T q
+//                               decay:  S = decay_h S + k v^T with a constant per head, y = S^T q (q, k, v through SiLU if asked)
+//                               channel delta: the delta form with one decay per head and key channel (rows of S)
+//   ms_low_rank_expand        the second product of a two-step (low-rank) projection, as it is, or turned into decays
 //   ms_head_norm_gate         y / bottom, divided by its root mean square per head, times a weight, times sigmoid or SiLU of a gate
 //   ms_gated_recurrence_scan  S = a S + sqrt(1 - a^2) i u per channel with a = exp(rate sigmoid(.)), times gelu_tanh of a branch
 //
@@ -107,7 +110,7 @@ __global__ void decay_gates_kernel(const float* __restrict__ logits, const float
 // way from memory into registers (kScanFetch keys, queries and values a thread: a chunk holds at most 256 kScanFetch of
 // each), so that the walk waits for memory once a request and not once a chunk.
 constexpr int kScanThreads = 256, kScanShift = 8;
-constexpr int kModeMemory = 0, kModeDelta = 1;
+constexpr int kModeMemory = 0, kModeDelta = 1, kModeDecay = 2, kModeChannelDelta = 3;
 constexpr int kPiecePad = 4;
 constexpr int kScanFetch = 8;
 
@@ -127,11 +130,15 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
                    const T* __restrict__ v, int v_ld, int v_col, float q_scale, const float* __restrict__ gates,
                    float* __restrict__ states, long long state_stride, int state_offset,
                    const int* __restrict__ state_slots, const int* __restrict__ query_start, int heads, int kv_heads, int dim,
-                   int vdim, int lpc_shift, int tok, float* __restrict__ y, float* __restrict__ bottom) {
+                   int vdim, int lpc_shift, int tok, float* __restrict__ y, float* __restrict__ bottom, int gate_ld,
+                   int gate_col, const float* __restrict__ channel_decay, int input_act) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ __align__(16) float matrix_smem[];
-  constexpr int G = MODE == kModeMemory ? 3 : 2;
+  // numbers of `gates` a token and head has: (keep, write, floor), (decay, beta), none (the decay is the head's constant:
+  // gates [heads]), or one logit whose sigmoid is beta (gates: rows of gate_ld numbers, the heads' logits from gate_col)
+  constexpr int G = MODE == kModeMemory ? 3 : MODE == kModeDelta ? 2 : MODE == kModeDecay ? 0 : 1;
+  constexpr bool CHANNEL = MODE == kModeChannelDelta;
   constexpr int PIECE = R + kPiecePad;
   const int LPC = 1 << lpc_shift, cols_per_block = kScanThreads >> lpc_shift;
   const int row = LPC * PIECE;                                // floats of a token's key (or query) in shared memory
@@ -147,6 +154,8 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
   float* qs = ks + tok * row;                                 // [tok][row]
   float* vs = qs + tok * row;                                 // [tok][cols_per_block]
   float* gs = vs + tok * cols_per_block;                      // [tok][4]
+  float* ds = gs + tok * 4;                                   // [tok][row]: the key channels' decays (channel delta only)
+  const float head_decay = MODE == kModeDecay ? gates[head] : 1.f;
   float* kept = states + (long long)state_slots[request] * state_stride + state_offset + ((size_t)head * columns + (active ? col : 0)) * dim;
   float s[R];
   // (a lane's piece as 16-byte accesses where it lies so: a column is `dim` floats, the state's row may start anywhere)
@@ -176,6 +185,9 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
   float* out_at = (sub == 0 && active) ? (is_n ? bottom + (size_t)q0 * heads + head : y + ((size_t)q0 * heads + head) * vdim + col) : nullptr;
   const size_t out_step = is_n ? (size_t)heads : (size_t)heads * vdim;
   T next_k[kScanFetch], next_q[kScanFetch], next_v[kScanFetch];
+  float next_d[CHANNEL ? kScanFetch : 1];
+  const float* d_head = CHANNEL ? channel_decay + (size_t)head * dim : nullptr;
+  const int d_ld = heads * dim;
   float next_g = 0.f;
   auto fetch = [&](int t0) {
     const int len = min(tok, q_len - t0);
@@ -186,13 +198,18 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
       const bool real = tt < len && i < dim;
       next_k[j] = real ? k_head[(first + tt) * k_ld + i] : from_float<T>(0.f);
       next_q[j] = real ? q_head[(first + tt) * q_ld + i] : from_float<T>(0.f);
+      if (CHANNEL) next_d[j] = real ? d_head[(first + tt) * d_ld + i] : 1.f;
     }
 #pragma unroll
     for (int j = 0; j < kScanFetch; ++j) {
       const int idx = tid + kScanThreads * j, tt = idx >> col_shift, c = idx & (cols_per_block - 1);
       next_v[j] = (tt < len && c < cols_here) ? v_head[(first + tt) * v_ld + c] : from_float<T>(1.f);      // (the column n)
     }
-    if (tid < len * G) next_g = gates[((first + tid / G) * heads + head) * G + tid % G];
+    if (CHANNEL) {
+      if (tid < len) next_g = sigmoid_f(gates[(first + tid) * gate_ld + gate_col + head]);
+    } else if (G > 0) {
+      if (tid < len * G) next_g = gates[((first + tid / (G > 0 ? G : 1)) * heads + head) * G + tid % (G > 0 ? G : 1)];
+    }
   };
   fetch(0);
   for (int t0 = 0; t0 < q_len; t0 += tok) {
@@ -203,16 +220,27 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
       const int idx = tid + kScanThreads * j, tt = idx >> dim_shift, i = idx & (dim_pad - 1);
       if (tt < len) {
         const int at = tt * row + (i >> LOG_R) * PIECE + (i & (R - 1));
-        ks[at] = to_float(next_k[j]);
-        qs[at] = q_scale * to_float(next_q[j]);
+        float key = to_float(next_k[j]), query = to_float(next_q[j]);
+        if (input_act) key *= sigmoid_f(key), query *= sigmoid_f(query);
+        ks[at] = key;
+        qs[at] = q_scale * query;
+        if (CHANNEL) ds[at] = next_d[j];
       }
     }
 #pragma unroll
     for (int j = 0; j < kScanFetch; ++j) {
       const int idx = tid + kScanThreads * j;
-      if ((idx >> col_shift) < len) vs[idx] = to_float(next_v[j]);
+      if ((idx >> col_shift) < len) {
+        float value = to_float(next_v[j]);
+        if (input_act) value *= sigmoid_f(value);
+        vs[idx] = value;
+      }
     }
-    if (tid < len * G) gs[(tid / G) * 4 + tid % G] = next_g;
+    if (CHANNEL) {
+      if (tid < len) gs[tid * 4 + 1] = next_g;
+    } else if (G > 0) {
+      if (tid < len * G) gs[(tid / (G > 0 ? G : 1)) * 4 + tid % (G > 0 ? G : 1)] = next_g;
+    }
     __syncthreads();
     if (t0 + tok < q_len) fetch(t0 + tok);
 #pragma unroll 4
@@ -222,8 +250,8 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
       const float value = vs[tt * cols_per_block + cc];
       const float4 gate = reinterpret_cast<const float4*>(gs)[tt];
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (MODE == kModeMemory) {
-        const float keep = gate.x, write = gate.y * value;
+      if (MODE == kModeMemory || MODE == kModeDecay) {
+        const float keep = MODE == kModeDecay ? head_decay : gate.x, write = MODE == kModeDecay ? value : gate.y * value;
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
           const float4 kv = kk[r >> 2], qv = qq[r >> 2];
@@ -238,14 +266,16 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
         }
       } else {
         const float decay = gate.x, beta = gate.y;
+        const float4* dd = reinterpret_cast<const float4*>(ds + tt * row + sub * PIECE);
         float seen[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
           const float4 kv = kk[r >> 2];
-          s[r] *= decay;
-          s[r + 1] *= decay;
-          s[r + 2] *= decay;
-          s[r + 3] *= decay;
+          const float4 dv = CHANNEL ? dd[r >> 2] : make_float4(decay, decay, decay, decay);
+          s[r] *= dv.x;
+          s[r + 1] *= dv.y;
+          s[r + 2] *= dv.z;
+          s[r + 3] *= dv.w;
           seen[0] += s[r] * kv.x;
           seen[1] += s[r + 1] * kv.y;
           seen[2] += s[r + 2] * kv.z;
@@ -288,6 +318,30 @@ matrix_scan_kernel(const T* __restrict__ q, int q_ld, int q_col, const T* __rest
       if (i < dim) kept[i] = s[r];
     }
   }
+}
+
+// The second product of a projection made in two steps through `rank` numbers: value[n, r] = sum_j mid[n, col + j] w[r, j]
+// with mid float32 (rows of ld numbers) and w float32 [rows, rank].  decay == 0: out[n, r] = value in the type T.
+// decay != 0 (T float): out[n, r] = exp(-exp(a_log[r / per_head]) softplus(value + bias[r])), a decay per head and channel.
+template <typename T>
+__global__ void low_rank_expand_kernel(const float* __restrict__ mid, int ld, int col, int rank, const float* __restrict__ w,
+                                       int rows, int decay, const float* __restrict__ a_log, const float* __restrict__ bias,
+                                       int per_head, T* __restrict__ out, long long total) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int r = (int)(i % rows);
+  const float* row = mid + (size_t)(i / rows) * ld + col;
+  float sum = 0.f;
+  if (w == nullptr) {
+    sum = row[r];                                             // (no second matrix: the numbers themselves)
+  } else {
+    const float* wr = w + (size_t)r * rank;
+    for (int j = 0; j < rank; ++j) sum += row[j] * wr[j];
+  }
+  if (decay) sum = expf(-expf(a_log[r / per_head]) * softplus_f(sum + bias[r]));
+  out[i] = from_float<T>(sum);
 }
 
 // One warp per (token, head): v = y / bottom, v / sqrt(mean(v^2) + eps) * weight * act(gate).  Where a head's row is
@@ -498,13 +552,19 @@ static int scan_sm_count() {
 // mode 0 (memory): gates [tokens, heads, 3], state [heads, vdim + 1, dim] per slot, bottom [tokens, heads];
 // mode 1 (delta): gates [tokens, heads, 2], state [heads, vdim, dim], bottom unused.  q, k, v: rows of q_ld, k_ld, v_ld
 // numbers of type `dtype`; y float32 [tokens, heads, vdim].  max_query_len: an upper bound of the tokens a request brings.
+// mode 2 (decay): gates [heads], the heads' constant decays; state [heads, vdim, dim].  mode 3 (channel delta): gates are rows
+// of gate_ld float32 numbers whose columns gate_col .. gate_col + heads hold the logits of beta; channel_decay float32
+// [tokens, heads, dim]; state [heads, vdim, dim].  input_act != 0: q, k and v pass SiLU as they are read.
 MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const void* k, int k_ld, int k_col, const void* v,
                              int v_ld, int v_col, int dtype, float q_scale, const float* gates, float* states,
                              long long state_stride, int state_offset, const int* state_slots, const int* query_start,
                              int n_requests, int max_query_len, int heads, int kv_heads, int dim, int vdim, float* y,
-                             float* bottom, cudaStream_t stream) {
+                             float* bottom, int gate_ld, int gate_col, const float* channel_decay, int input_act,
+                             cudaStream_t stream) {
   if (n_requests == 0 || max_query_len <= 0 || heads == 0) return 0;
-  MS_REQUIRE(mode == kModeMemory || mode == kModeDelta, "matrix_scan: mode %d", mode);
+  MS_REQUIRE(mode >= kModeMemory && mode <= kModeChannelDelta, "matrix_scan: mode %d", mode);
+  MS_REQUIRE(mode != kModeChannelDelta || (channel_decay != nullptr && gate_col >= 0 && gate_col + heads <= gate_ld),
+             "matrix_scan: the channel form needs the channels' decays and the heads' logits (columns %d.. of %d)", gate_col, gate_ld);
   MS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0 && dim >= 1 && dim <= 512 && vdim >= 1, "matrix_scan: %d/%d heads of %d/%d",
              heads, kv_heads, dim, vdim);
   MS_REQUIRE(mode != kModeMemory || bottom != nullptr, "matrix_scan: the memory form writes the tokens' divisors");
@@ -531,7 +591,7 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
   const int r = piece(lpc_shift);
   const int cols_per_block = kScanThreads >> lpc_shift;
   const int columns = mode == kModeMemory ? vdim + 1 : vdim;
-  const int row_floats = 2 * ((r + kPiecePad) << lpc_shift) + cols_per_block + 4;
+  const int row_floats = (mode == kModeChannelDelta ? 3 : 2) * ((r + kPiecePad) << lpc_shift) + cols_per_block + 4;
   // a chunk: at most 16 tokens, kScanThreads kScanFetch keys and as many values (what the threads hold of the next chunk)
   // and 40 KB of shared memory
   int tok = max_query_len < 16 ? max_query_len : 16;
@@ -545,16 +605,42 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
   MS_REC_DISPATCH(dtype, (ms::launch(matrix_scan_kernel<T, R, MODE>, grid, kScanThreads, smem, stream, (const T*)q, q_ld, q_col, \
                                      (const T*)k, k_ld, k_col, (const T*)v, v_ld, v_col, q_scale, gates, states, state_stride,  \
                                      state_offset, state_slots, query_start, heads, kv_heads, dim, vdim, lpc_shift, tok, y,     \
-                                     bottom)))
+                                     bottom, gate_ld, gate_col, channel_decay, input_act)))
   if (mode == kModeMemory) {
     if (r == 4) { MS_MATRIX_SCAN(4, kModeMemory); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeMemory); }
     else if (r == 16) { MS_MATRIX_SCAN(16, kModeMemory); } else { MS_MATRIX_SCAN(32, kModeMemory); }
+  } else if (mode == kModeDecay) {
+    if (r == 4) { MS_MATRIX_SCAN(4, kModeDecay); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeDecay); }
+    else if (r == 16) { MS_MATRIX_SCAN(16, kModeDecay); } else { MS_MATRIX_SCAN(32, kModeDecay); }
+  } else if (mode == kModeChannelDelta) {
+    if (r == 4) { MS_MATRIX_SCAN(4, kModeChannelDelta); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeChannelDelta); }
+    else if (r == 16) { MS_MATRIX_SCAN(16, kModeChannelDelta); } else { MS_MATRIX_SCAN(32, kModeChannelDelta); }
   } else {
     if (r == 4) { MS_MATRIX_SCAN(4, kModeDelta); } else if (r == 8) { MS_MATRIX_SCAN(8, kModeDelta); }
     else if (r == 16) { MS_MATRIX_SCAN(16, kModeDelta); } else { MS_MATRIX_SCAN(32, kModeDelta); }
   }
 #undef MS_MATRIX_SCAN
   MS_CHECK_LAUNCH("matrix_scan");
+  return 0;
+}
+
+// mid float32 rows of ld numbers (the first product's results from column col); w float32 [rows, rank]; out [tokens, rows] of
+// type `dtype`, or, decay != 0, float32 decays exp(-exp(a_log[row / per_head]) softplus(. + bias[row])).  w null (rank == rows):
+// the numbers of mid themselves take the place of the product.
+MS_EXPORT int ms_low_rank_expand(const float* mid, int ld, int col, int rank, const float* w, int rows, int decay,
+                                 const float* a_log, const float* bias, int per_head, void* out, int dtype, int n_tokens,
+                                 cudaStream_t stream) {
+  const long long total = (long long)n_tokens * rows;
+  if (total == 0) return 0;
+  MS_REQUIRE(rank >= 1 && col >= 0 && col + rank <= ld, "low_rank_expand: %d numbers from column %d of rows of %d", rank, col, ld);
+  MS_REQUIRE(w != nullptr || rank == rows, "low_rank_expand: without a second matrix the %d numbers are the %d results", rank, rows);
+  MS_REQUIRE(!decay || (a_log && bias && per_head >= 1 && rows % per_head == 0 && dtype == MS_F32),
+             "low_rank_expand: decays are float32 and need A_log, a bias and the heads' size (%d rows, %d a head)", rows, per_head);
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "low_rank_expand: %lld numbers in one launch is too many", total);
+  MS_REC_DISPATCH(dtype, (ms::launch(low_rank_expand_kernel<T>, (unsigned)blocks, 256, 0, stream, mid, ld, col, rank, w, rows, decay,
+                                     a_log, bias, per_head, (T*)out, total)));
+  MS_CHECK_LAUNCH("low_rank_expand");
   return 0;
 }
 

@@ -28,13 +28,13 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 // only block that reads the old one (into registers, before anything is written), so nothing races.
 // `in_bias` (or null) is added to every input read from `proj` (the bias of the projection that made it; the state keeps
 // inputs with it, and the zeros before a sequence's start stay zeros); `bias` (or null) is the convolution's own.
-template <typename T>
+template <typename T, typename U>
 __global__ void __launch_bounds__(128)
 causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channels, int taps,
                         const float* __restrict__ weight, const float* __restrict__ bias,
                         const float* __restrict__ in_bias, int activation, float* __restrict__ states,
                         long long state_stride, int state_offset, const int* __restrict__ state_slots,
-                        const int* __restrict__ query_start, float* __restrict__ out) {
+                        const int* __restrict__ query_start, U* __restrict__ out) {
   grid_dependency_wait();
   grid_dependency_launch();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -88,7 +88,7 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
       if (k == taps - 1) window[k] = u;
       if (k < taps) sum += w[k] * window[k];
     }
-    out[(size_t)(q0 + t) * channels + c] = activation ? silu_f(sum) : sum;
+    out[(size_t)(q0 + t) * channels + c] = from_float<U>(activation ? silu_f(sum) : sum);
   }
 }
 
@@ -408,20 +408,26 @@ using namespace ms;
 // proj [tokens, ld]: the convolution's inputs are its columns col .. col + channels; weight float32 [channels, taps] (the
 // last tap is the current token's), bias float32 [channels] or null; in_bias float32 [channels] or null (added to the inputs
 // as they are read); activation 0: none, 1: SiLU; states float32, one row of state_stride numbers per slot, the
-// convolution's part at state_offset; out float32 [tokens, channels].
+// convolution's part at state_offset; out [tokens, channels], float32 or (out_like_proj != 0) of proj's type.
 MS_EXPORT int ms_causal_conv(const void* proj, int dtype, int ld, int col, int channels, int taps, const float* weight,
                              const float* bias, const float* in_bias, int activation, float* states, long long state_stride,
                              int state_offset, const int* state_slots, const int* query_start, int n_requests,
-                             int max_query_len, float* out, cudaStream_t stream) {
+                             int max_query_len, void* out, int out_like_proj, cudaStream_t stream) {
   if (n_requests == 0 || max_query_len == 0 || channels == 0) return 0;
   MS_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal_conv: %d taps outside 1..%d", taps, kMaxTaps);
   MS_REQUIRE(activation == 0 || activation == 1, "causal_conv: activation code %d", activation);
   const int chunks = (max_query_len + kConvTokens - 1) / kConvTokens;
   MS_REQUIRE(chunks <= 65535 && n_requests <= 65535, "causal_conv: grid %d x %d exceeds the launch limits", chunks, n_requests);
   dim3 grid((channels + 127) / 128, chunks, n_requests);
-  MS_SS_DISPATCH(dtype, (ms::launch(causal_conv_silu_kernel<T>, grid, 128, 0, stream, (const T*)proj, ld, col, channels, taps,
-                                    weight, bias, in_bias, activation, states, state_stride, state_offset, state_slots,
-                                    query_start, out)));
+  if (out_like_proj) {
+    MS_SS_DISPATCH(dtype, (ms::launch(causal_conv_silu_kernel<T, T>, grid, 128, 0, stream, (const T*)proj, ld, col, channels, taps,
+                                      weight, bias, in_bias, activation, states, state_stride, state_offset, state_slots,
+                                      query_start, (T*)out)));
+  } else {
+    MS_SS_DISPATCH(dtype, (ms::launch(causal_conv_silu_kernel<T, float>, grid, 128, 0, stream, (const T*)proj, ld, col, channels, taps,
+                                      weight, bias, in_bias, activation, states, state_stride, state_offset, state_slots,
+                                      query_start, (float*)out)));
+  }
   MS_CHECK_LAUNCH("causal_conv");
   return 0;
 }

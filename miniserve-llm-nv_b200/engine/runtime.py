@@ -111,12 +111,16 @@ def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size
 
     chosen = []
     pairs = []
-    for index, run in enumerate(model.spec.order):
-        plan, mixer = model.run_caches[index], model.blocks[run.layer].mixer
+
+    def flatten(plan, mixer):
         if isinstance(plan, tuple):          # a mixer of several members, each with its own cache
-            pairs.extend(zip(plan, mixer.members))
+            for member_plan, member in zip(plan, mixer.cache_members()):
+                flatten(member_plan, member)
         else:
             pairs.append((plan, mixer))
+
+    for index, run in enumerate(model.spec.order):
+        flatten(model.run_caches[index], model.blocks[run.layer].mixer)
     for plan, mixer in pairs:
         if plan is None or not plan.writable or plan.slot != 0:
             continue
@@ -136,7 +140,7 @@ def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size
         n_q = getattr(mixer, "num_heads", need.num_kv_heads)
         modified = bool(getattr(mixer, "score_softcap", None)) or getattr(mixer, "score_bias_slopes", None) is not None
         names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size, modified, need.value_dim,
-                                          bool(getattr(mixer, "general", False)))
+                                          bool(getattr(mixer, "general", False)), need.chunk)
         chosen.append(dict(group=plan.group, head_dim=need.head_dim, window=need.window, **names))
         slow = dtype == torch.bfloat16 and "general" in names.values()
         log.log(logging.WARNING if slow else logging.INFO,

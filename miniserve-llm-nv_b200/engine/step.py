@@ -62,7 +62,7 @@ class DecodeGraph:
         self.copied: Optional[torch.cuda.Event] = None     # recorded after the last copy of the host mirror
         # per row: (the request's cache record, pages of its committed table that the mirror shows, per group)
         self.row_owner: list = [None] * rows
-        self.has_windows = any(need.window is not None for need in manager.paged_needs)
+        self.has_windows = any(not need.keeps_all for need in manager.paged_needs)
         self.meta = torch.zeros(self.offsets[-1], dtype=torch.int32, device=sf.device)
         self.n_groups = n_groups
         self.scratch = storage.scratch_page

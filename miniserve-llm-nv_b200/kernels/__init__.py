@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -157,10 +157,11 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 def postnorm_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
                          post_eps: float, weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
-                         rows: Optional[torch.Tensor] = None, post_scale: float = 1.0) -> None:
+                         rows: Optional[torch.Tensor] = None, post_scale: float = 1.0, post_norm: bool = True) -> None:
     """``residual += post_scale * post_weight * delta / rms(delta)`` (float32, in place), ``out = weight * residual /
     rms(residual)``: a sublayer's output passes a norm of its own on its way into the stream, and the stream is normed for
-    the next sublayer.  ``delta`` None: nothing is added.  ``weight`` None: the stream is not normed, ``out`` is the stream
+    the next sublayer.  ``post_norm=False``: the output is not divided by its root mean square, ``residual += post_scale *
+    post_weight * delta`` (a scale per channel on what a sublayer adds).  ``delta`` None: nothing is added.  ``weight`` None: the stream is not normed, ``out`` is the stream
     rounded once to ``out``'s type (a sublayer that reads the stream itself).  With ``rows`` (int32 ``[K]``) only those
     rows are computed, into ``out [K, H]``, and the residual is left untouched.  The weights may be float32 or bfloat16
     whatever ``out`` is."""
@@ -177,26 +178,35 @@ def postnorm_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], 
         _want(rows, "rows", torch.int32)
     _check(library().ms_postnorm_add_rmsnorm(
         _ptr(residual), _ptr(delta), _i(_code(out.dtype)), _ptr(post_weight) if delta is not None else None,
-        _i(_code(post_weight.dtype)) if delta is not None else 0, _f(post_eps), _f(post_scale), _ptr(weight),
+        _i(_code(post_weight.dtype)) if delta is not None else 0, _f(post_eps if post_norm else -1.0), _f(post_scale), _ptr(weight),
         _i(_code(weight.dtype)) if weight is not None else 0, _f(eps), _ptr(rows), _ptr(out), _i(n_out), _i(hidden), _stream()))
 
 
 def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int, n_kv: int, head_dim: int, value_dim: int,
                 slots: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                 cos_sin: Optional[torch.Tensor], rotary_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                q_out: torch.Tensor, interleaved: bool = False) -> None:
+                q_out: torch.Tensor, interleaved: bool = False, bias: Optional[torch.Tensor] = None,
+                value_heads: Optional[int] = None) -> None:
     """Per-head RMSNorm of q and k, rotation of their first ``rotary_dim`` entries (entry i with entry i + rotary_dim / 2,
     or, ``interleaved``, entry 2i with entry 2i + 1), and the append of k and v
     to one layer's pools, for a projection ``proj [N, ld]`` whose columns are laid out freely: query head h at
     ``q_col + h * head_dim``, key head g at ``k_col + g * head_dim``, value head g at ``v_col + g * value_dim``.
     ``k_col < 0``: the projection holds no keys and values (the layer reads another layer's) and only ``q_out
     [N, n_q, head_dim]`` is written.  Key pool ``[pages, n_kv, page_size, head_dim]``, value pool ``[.., value_dim]``;
-    norm weights float32 ``[head_dim]`` or None; ``cos_sin`` float32 ``[N, rotary_dim / 2, 2]`` or None."""
+    norm weights float32 ``[head_dim]`` or None; ``cos_sin`` float32 ``[N, rotary_dim / 2, 2]`` or None.  ``bias`` (float32
+    ``[ld]``, column by column as ``proj``): the projection's bias, added in float32 as the heads are read.  ``value_heads``
+    (a divisor of ``n_kv``; None: ``n_kv``): the projection holds that many value heads, and the pool's value head g receives
+    head ``g % value_heads`` (key heads that share values)."""
     n, ld = proj.shape
+    value_heads = n_kv if value_heads is None else int(value_heads)
+    if value_heads < 1 or n_kv % value_heads:
+        raise KernelError(f"qkv_prepare: {value_heads} value heads for {n_kv} key heads")
+    if bias is not None:
+        _want(bias, "bias", torch.float32, (ld,))
     _want(proj, "proj")
     _want(q_out, "q_out", proj.dtype, (n, n_q, head_dim))
     own = k_col >= 0
-    if q_col < 0 or q_col + n_q * head_dim > ld or (own and (k_col + n_kv * head_dim > ld or v_col < 0 or v_col + n_kv * value_dim > ld)):
+    if q_col < 0 or q_col + n_q * head_dim > ld or (own and (k_col + n_kv * head_dim > ld or v_col < 0 or v_col + value_heads * value_dim > ld)):
         raise KernelError(f"qkv_prepare: columns {q_col}, {k_col}, {v_col} of {n_q}/{n_kv} heads of {head_dim}/{value_dim} in rows of {ld}")
     if own:
         _want(slots, "slots", torch.int32, (n,))
@@ -216,7 +226,7 @@ def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int
         _ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(q_col), _i(k_col if own else -1), _i(v_col if own else -1), _i(n_q), _i(n_kv),
         _i(head_dim), _i(value_dim), _ptr(slots) if own else None, _ptr(q_weight), _ptr(k_weight) if own else None, _f(eps),
         _ptr(cos_sin), _i(rotary_dim), _ptr(k_pool) if own else None, _ptr(v_pool) if own else None,
-        _i(k_pool.shape[2]) if own else 1, _ptr(q_out), _i(n), _i(1 if interleaved else 0), _stream()))
+        _i(k_pool.shape[2]) if own else 1, _ptr(q_out), _i(n), _i(1 if interleaved else 0), _ptr(bias), _i(value_heads), _stream()))
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos_sin: torch.Tensor, magnitude: float = 1.0) -> None:
@@ -299,6 +309,93 @@ def scaled_sum(a: torch.Tensor, a_scale: float, b: torch.Tensor, b_scale: float,
     _check(library().ms_scaled_sum(_ptr(a), _f(a_scale), _ptr(b), _f(b_scale), _ptr(out), _i(_code(a.dtype)), a.numel(), _stream()))
 
 
+def normed_sum(a: torch.Tensor, a_weight: torch.Tensor, a_scale: float, b: torch.Tensor, b_weight: torch.Tensor, b_scale: float,
+               eps: float, out: torch.Tensor) -> None:
+    """``out = a_scale * a_weight * a / rms(a) + b_scale * b_weight * b / rms(b)`` row by row (``eps`` inside the roots): two
+    outputs, each normed over the row with a float32 weight of its own, summed."""
+    rows, hidden = a.shape
+    _want(a, "a")
+    _want(b, "b", a.dtype, a.shape)
+    _want(out, "out", a.dtype, a.shape)
+    _want(a_weight, "a_weight", torch.float32, (hidden,))
+    _want(b_weight, "b_weight", torch.float32, (hidden,))
+    _check(library().ms_normed_sum(_ptr(a), _ptr(a_weight), _f(a_scale), _ptr(b), _ptr(b_weight), _f(b_scale), _f(eps), _ptr(out),
+                                   _i(_code(a.dtype)), _i(rows), _i(hidden), _stream()))
+
+
+def sigmoid_gate_mul(x: torch.Tensor, gate: torch.Tensor, gate_col: int, out: torch.Tensor) -> None:
+    """``out[n, c] = x[n, c] * sigmoid(gate[n, gate_col + c])``: a gate per entry; ``out`` may be ``x``."""
+    rows, width = x.shape
+    _want(x, "x")
+    _want(gate, "gate", x.dtype)
+    _want(out, "out", x.dtype, x.shape)
+    if gate.dim() != 2 or gate.shape[0] != rows or gate_col < 0 or gate_col + width > gate.shape[1]:
+        raise KernelError(f"sigmoid_gate_mul: gate {tuple(gate.shape)} from column {gate_col} for rows of {width}")
+    _check(library().ms_sigmoid_gate_mul(_ptr(x), _ptr(gate), _i(gate.shape[1]), _i(gate_col), _ptr(out), _i(_code(x.dtype)), _i(rows),
+                                         _i(width), _stream()))
+
+
+def differential_combine(a: torch.Tensor, lam: float, eps: float, out_scale: float, gate: Optional[torch.Tensor], gate_col: int,
+                         out: torch.Tensor) -> None:
+    """``a [N, 2 H, dv]`` holds the outputs of two score maps over the same values (the first map's heads, then the second's):
+    ``o = a[:, h] - lam * a[:, H + h]``, each head divided by its root mean square (``eps`` inside the root), times ``out_scale``,
+    times ``sigmoid(gate[n, gate_col + h dv + c])`` where ``gate`` is given.  ``out [N, H, dv]``."""
+    n, both, dv = a.shape
+    heads = both // 2
+    _want(a, "a")
+    _want(out, "out", a.dtype, (n, heads, dv))
+    gate_ld = 0
+    if gate is not None:
+        _want(gate, "gate", a.dtype)
+        if gate.dim() != 2 or gate.shape[0] != n or gate_col < 0 or gate_col + heads * dv > gate.shape[1]:
+            raise KernelError(f"differential_combine: gate {tuple(gate.shape)} from column {gate_col} for {heads} heads of {dv}")
+        gate_ld = gate.shape[1]
+    if both != 2 * heads:
+        raise KernelError(f"differential_combine: {both} heads are not two maps")
+    _check(library().ms_differential_combine(_ptr(a), _i(heads), _i(dv), _f(lam), _f(eps), _f(out_scale), _ptr(gate), _i(gate_ld),
+                                             _i(gate_col), _ptr(out), _i(_code(a.dtype)), _i(n), _stream()))
+
+
+def token_shift(x: torch.Tensor, shift: torch.Tensor, states: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
+                query_start: torch.Tensor, request_of_token: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t] = x[t] + (x[t - 1] - x[t]) * shift`` per channel along each request's tokens; the token before a portion's
+    first is what ``states[slot, state_offset:]`` (float32 ``[hidden]``, zero for a new sequence) holds, and the portion's last
+    ``x`` is left there.  ``shift`` float32 ``[hidden]``; ``out`` is not ``x``."""
+    n, hidden = x.shape
+    _want(x, "x")
+    _want(out, "out", x.dtype, x.shape)
+    _want(shift, "shift", torch.float32, (hidden,))
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    _want(request_of_token, "request_of_token", torch.int32, (n,))
+    stride = _state_rows(states, state_offset, hidden)
+    _check(library().ms_token_shift(_ptr(x), _i(_code(x.dtype)), _ptr(shift), _ptr(states), stride, _i(state_offset),
+                                    _ptr(state_slots), _ptr(query_start), _ptr(request_of_token), _ptr(out), _i(n), _i(hidden),
+                                    _stream()))
+
+
+def pair_embedding(tokens: torch.Tensor, table: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int, states: torch.Tensor,
+                   state_slots: torch.Tensor, query_start: torch.Tensor, request_of_token: torch.Tensor,
+                   residual: torch.Tensor) -> None:
+    """``residual[t] += table[(token[t - 1] * mul_prev + token[t] * mul_cur) % buckets]``; a sequence's first token takes row
+    ``buckets``.  ``states`` int32 ``[slots, 1]`` holds each request's last token + 1 (0: none yet) and is updated."""
+    n, hidden = residual.shape
+    _want(tokens, "tokens", torch.int32, (n,))
+    _want(table, "table", None, (buckets + 1, hidden))
+    _want(residual, "residual", torch.float32)
+    _want(states, "states", torch.int32)
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    _want(request_of_token, "request_of_token", torch.int32, (n,))
+    if states.dim() != 2 or states.shape[1] < 1:
+        raise KernelError(f"pair_embedding: states {tuple(states.shape)} do not hold a token per slot")
+    _check(library().ms_pair_embedding(_ptr(tokens), _ptr(table), _i(_code(table.dtype)), _i(buckets), _i(mul_prev), _i(mul_cur),
+                                       _ptr(states), states.shape[1], _i(0), _ptr(state_slots), _ptr(query_start),
+                                       _ptr(request_of_token), _ptr(residual), _i(n), _i(hidden), _stream()))
+
+
 # --------------------------------------------------------------------------- attention
 
 MAX_HEAD_DIM = 512      # of the general attention kernel (attention_generic.cu: 16 output lanes per thread)
@@ -308,19 +405,21 @@ USE_MMA_ANY = __import__("os").environ.get("MINISERVE_B200_MMA_ANY", "1") == "1"
 
 
 def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, page_size: int,
-                      modified_scores: bool = False, value_dim: Optional[int] = None, extended: bool = False) -> dict:
+                      modified_scores: bool = False, value_dim: Optional[int] = None, extended: bool = False,
+                      chunk: Optional[int] = None) -> dict:
     """Which kernel :func:`paged_attention` runs for these sizes: ``{"decode": name, "prompt": name}`` with the
     names ``tcgen05``, ``mma.sync`` and ``general`` (float32 arithmetic, any size; the only one of the float32
     path, and what bfloat16 falls back to for head sizes the tensor-core kernels are not built for and for
     scores with a soft cap or a distance bias)."""
     lib = library()
     value_dim = head_dim if value_dim is None else value_dim
+    extended = extended or bool(chunk)
     if (USE_MMA_ANY and extended and not modified_scores and dtype == torch.bfloat16
-            and (value_dim != head_dim or not lib.ms_attention_mma_supports(_i(head_dim)))
+            and (value_dim != head_dim or bool(chunk) or not lib.ms_attention_mma_supports(_i(head_dim)))
             and lib.ms_attention_mma_any_supports(_i(head_dim), _i(value_dim))):
         # (``extended``: the attention has a sink, a gate or value heads of their own size)
         return {"decode": "mma.sync (any size)", "prompt": "mma.sync (any size)"}
-    if modified_scores or value_dim != head_dim or dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+    if modified_scores or value_dim != head_dim or chunk or dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         return {"decode": "general", "prompt": "general"}
     prompt = "mma.sync"
     if USE_TCGEN05_ATTENTION and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(page_size)):
@@ -334,8 +433,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     context_lens: torch.Tensor, max_query_len: int, max_context_len: int, scale: float,
                     window: Optional[int], out: torch.Tensor, host_query_start: Optional[list] = None,
                     softcap: Optional[float] = None, bias_slopes: Optional[torch.Tensor] = None, sink: bool = False,
-                    gate: Optional[torch.Tensor] = None, gate_col: int = 0) -> None:
+                    gate: Optional[torch.Tensor] = None, gate_col: int = 0, chunk: Optional[int] = None) -> None:
     """Causal grouped-query attention of every token over its request's paged keys and values.
+
+    ``chunk``: a token at position p sees only the keys of its own chunk, ``p - p % chunk .. p`` (chunks are counted from
+    position 0 of the sequence).  The general kernel and the tensor-core kernel for any head size implement it.
 
     q ``[N, n_q, d]``, out ``[N, n_q, dv]`` (dv: the value pool's last dimension, usually d); pools of one layer
     ``[pages, n_kv, page_size, d | dv]``.  ``sink``: the softmax's denominator gets one more term ``exp(0)`` (a key of
@@ -387,13 +489,14 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _want(bias_slopes, "bias_slopes", torch.float32, (n_q,))
     # the general form (a sink, a gate, value heads of their own size) at sizes the unrolled tensor-core kernels are not built
     # for: the tensor-core kernel whose head sizes are run-time numbers (multiples of 16 up to 128)
-    extended = sink or gate is not None or value_dim != head_dim
+    extended = sink or gate is not None or value_dim != head_dim or bool(chunk)
     if (USE_MMA_ANY and extended and not modified and q.dtype == torch.bfloat16
-            and (value_dim != head_dim or not lib.ms_attention_mma_supports(_i(head_dim)))
+            and (value_dim != head_dim or bool(chunk) or not lib.ms_attention_mma_supports(_i(head_dim)))
             and lib.ms_attention_mma_any_supports(_i(head_dim), _i(value_dim))):
+        reach = min(max_context_len, chunk) if chunk else max_context_len      # the most keys a token sees
         def run_any(first: int, last: int, longest: int, rows: int, first_row: int = 0) -> None:
             count = last - first
-            splits = lib.ms_attention_mma_any_splits(_i(count), _i(n_kv), _i(n_q), _i(longest), _i(max_context_len))
+            splits = lib.ms_attention_mma_any_splits(_i(count), _i(n_kv), _i(n_q), _i(longest), _i(reach))
             part_o = part_lse = None
             if splits > 1:
                 part_o = torch.empty((rows * n_q * splits, value_dim), dtype=torch.float32, device=q.device)
@@ -402,7 +505,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables[first:last]), _i(block_tables.shape[1]),
                 _ptr(query_start[first:last + 1]), _ptr(context_lens[first:last]), _i(k_pool.shape[2]), _i(n_q), _i(n_kv),
                 _i(head_dim), _i(value_dim), _f(scale), _i(window if window else 0), _ptr(out), _ptr(part_o), _ptr(part_lse),
-                _i(splits), _i(count), _i(longest), _i(rows), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(first_row), _stream()))
+                _i(splits), _i(count), _i(longest), _i(rows), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(first_row),
+                _i(chunk or 0), _stream()))
 
         single = 0
         if host_query_start and max_query_len > 1 and len(host_query_start) == n_requests + 1:
@@ -414,13 +518,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         else:
             run_any(0, n_requests, max_query_len, n)
         return
-    general = modified or value_dim != head_dim      # (the unrolled tensor-core kernels take the sink and the gate, not these)
+    general = modified or value_dim != head_dim or bool(chunk)      # (the unrolled tensor-core kernels take the sink and the gate, not these)
     if general or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         _check(lib.ms_paged_attention_generic(
             _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
             _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim),
             _f(scale), _i(window if window else 0), _f(softcap if softcap else 0.0), _ptr(bias_slopes), _ptr(out),
-            _i(n), _i(value_dim), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _stream()))
+            _i(n), _i(value_dim), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(chunk or 0), _stream()))
         return
 
     def run(first: int, last: int, longest: int, rows: int, first_row: int = 0) -> None:
@@ -681,7 +785,7 @@ def causal_conv(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: Option
     projection that made them; the zeros before a sequence's start do not get it); inputs before the portion come from
     ``states[slot, state_offset:]`` (float32 ``[taps - 1, channels]``, oldest first), which afterwards holds the last
     ``taps - 1`` inputs seen.  ``weight`` float32 ``[channels, taps]``, ``bias`` float32 ``[channels]`` or None;
-    ``state_slots`` int32 ``[R]``, ``query_start`` int32 ``[R + 1]``; ``out`` float32 ``[N, channels]``."""
+    ``state_slots`` int32 ``[R]``, ``query_start`` int32 ``[R + 1]``; ``out [N, channels]`` float32 or of ``proj``'s type."""
     n, ld = proj.shape
     channels, taps = weight.shape
     _want(proj, "proj")
@@ -689,7 +793,9 @@ def causal_conv(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: Option
     for name, tensor in (("bias", bias), ("in_bias", in_bias)):
         if tensor is not None:
             _want(tensor, name, torch.float32, (channels,))
-    _want(out, "out", torch.float32, (n, channels))
+    _want(out, "out", None, (n, channels))
+    if out.dtype not in (torch.float32, proj.dtype):
+        raise KernelError(f"causal_conv: out is float32 or {proj.dtype}, got {out.dtype}")
     n_requests = state_slots.numel()
     _want(state_slots, "state_slots", torch.int32)
     _want(query_start, "query_start", torch.int32, (n_requests + 1,))
@@ -699,7 +805,7 @@ def causal_conv(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: Option
     _check(library().ms_causal_conv(_ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(col), _i(channels), _i(taps), _ptr(weight),
                                     _ptr(bias), _ptr(in_bias), _i(CONV_ACTIVATIONS[activation]), _ptr(states), stride,
                                     _i(state_offset), _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(max_query_len),
-                                    _ptr(out), _stream()))
+                                    _ptr(out), _i(0 if out.dtype == torch.float32 else 1), _stream()))
 
 
 def selective_scan(conv: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
@@ -750,7 +856,7 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col: int, weight: to
 # --------------------------------------------------------------------------- recurrences that carry a matrix or a vector
 
 MAX_MATRIX_SCAN_DIM = 512     # entries of a query or key that matrix_scan spreads over a column's lanes (16 lanes x 32)
-MATRIX_SCAN_MODES = {"memory": 0, "delta": 1}
+MATRIX_SCAN_MODES = {"memory": 0, "delta": 1, "decay": 2, "channel_delta": 3}
 HEAD_GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
 
 
@@ -809,7 +915,8 @@ def decay_gates(logits: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor
 def matrix_scan(mode: str, q: torch.Tensor, q_col: int, k: torch.Tensor, k_col: int, v: torch.Tensor, v_col: int,
                 gates: torch.Tensor, states: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
                 query_start: torch.Tensor, max_query_len: int, heads: int, kv_heads: int, dim: int, vdim: int, y: torch.Tensor,
-                q_scale: float = 1.0, bottom: Optional[torch.Tensor] = None) -> None:
+                q_scale: float = 1.0, bottom: Optional[torch.Tensor] = None, gate_col: int = 0,
+                channel_decay: Optional[torch.Tensor] = None, input_activation: str = "none") -> None:
     """A recurrence that carries a ``dim x vdim`` matrix ``S`` per head, walked over each request's tokens from and into the
     request's state.  Queries and keys of head j are the columns ``q_col + (j // (heads / kv_heads)) dim ..`` of ``q`` (and
     ``k``), its values the columns ``v_col + j vdim ..`` of ``v`` (``q``, ``k``, ``v``: one 2-d tensor, float32 or the compute
@@ -818,7 +925,11 @@ def matrix_scan(mode: str, q: torch.Tensor, q_col: int, k: torch.Tensor, k_col: 
     ``"memory"``: ``gates [N, H, 3]`` = (keep, write, floor); ``S = keep S + write k v^T``, ``n = keep n + write k``, ``y = S^T q``
     and ``bottom [N, H] = max(|n . q|, floor) + 1e-6``.  The state holds ``[H, vdim + 1, dim]``: the columns of ``S``, then ``n``.
     ``"delta"``: ``gates [N, H, 2]`` = (decay, beta); ``S = decay S``, ``u = beta (v - S^T k)``, ``S = S + k u^T``, ``y = S^T q``.
-    The state holds ``[H, vdim, dim]``.  ``y`` float32 ``[N, H, vdim]``."""
+    The state holds ``[H, vdim, dim]``.  ``y`` float32 ``[N, H, vdim]``.
+    ``"decay"``: ``gates [H]``, a constant decay per head; ``S = decay S + k v^T``, ``y = S^T q`` (a linear attention).
+    ``"channel_delta"``: the delta form with a decay per head and key channel, ``channel_decay`` float32 ``[N, H * dim]``, acting on
+    the rows of ``S``; ``gates`` is float32 ``[N, ld]`` whose columns ``gate_col .. gate_col + H`` hold the logits of beta.  Both
+    keep ``[H, vdim, dim]``.  ``input_activation="silu"``: q, k and v pass SiLU as they are read."""
     code = MATRIX_SCAN_MODES[mode]
     n = y.shape[0]
     for name, tensor in (("q", q), ("k", k), ("v", v)):
@@ -828,7 +939,17 @@ def matrix_scan(mode: str, q: torch.Tensor, q_col: int, k: torch.Tensor, k_col: 
     if (heads % kv_heads or q_col < 0 or k_col < 0 or v_col < 0 or q_col + kv_heads * dim > q.shape[1]
             or k_col + kv_heads * dim > k.shape[1] or v_col + heads * vdim > v.shape[1] or not 1 <= dim <= MAX_MATRIX_SCAN_DIM):
         raise KernelError(f"matrix_scan: {heads}/{kv_heads} heads of {dim}/{vdim} at columns {q_col}, {k_col}, {v_col}")
-    _want(gates, "gates", torch.float32, (n, heads, 3 if code == 0 else 2))
+    gate_ld = 0
+    if code == 2:
+        _want(gates, "gates", torch.float32, (heads,))
+    elif code == 3:
+        _want(gates, "gates", torch.float32)
+        _want(channel_decay, "channel_decay", torch.float32, (n, heads * dim))
+        if gates.dim() != 2 or gates.shape[0] != n or gate_col < 0 or gate_col + heads > gates.shape[1]:
+            raise KernelError(f"matrix_scan: the logits of beta from column {gate_col} of {tuple(gates.shape)} for {heads} heads")
+        gate_ld = gates.shape[1]
+    else:
+        _want(gates, "gates", torch.float32, (n, heads, 3 if code == 0 else 2))
     _want(y, "y", torch.float32, (n, heads, vdim))
     if code == 0:
         _want(bottom, "bottom", torch.float32, (n, heads))
@@ -840,7 +961,40 @@ def matrix_scan(mode: str, q: torch.Tensor, q_col: int, k: torch.Tensor, k_col: 
     _check(library().ms_matrix_scan(_i(code), _ptr(q), _i(q.shape[1]), _i(q_col), _ptr(k), _i(k.shape[1]), _i(k_col), _ptr(v),
                                     _i(v.shape[1]), _i(v_col), _i(_code(q.dtype)), _f(q_scale), _ptr(gates), _ptr(states), stride,
                                     _i(state_offset), _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(max_query_len),
-                                    _i(heads), _i(kv_heads), _i(dim), _i(vdim), _ptr(y), _ptr(bottom), _stream()))
+                                    _i(heads), _i(kv_heads), _i(dim), _i(vdim), _ptr(y), _ptr(bottom), _i(gate_ld), _i(gate_col),
+                                    _ptr(channel_decay) if code == 3 else None, _i(CONV_ACTIVATIONS[input_activation]), _stream()))
+
+
+def channel_decays(logits: torch.Tensor, col: int, a_log: torch.Tensor, dt_bias: torch.Tensor, per_head: int, out: torch.Tensor) -> None:
+    """``out[n, r] = exp(-exp(a_log[r // per_head]) softplus(logits[n, col + r] + dt_bias[r]))``: a decay per head and channel
+    from float32 logits ``[N, ld]``; ``out`` float32 ``[N, R]``."""
+    n, ld = logits.shape
+    rows = out.shape[1]
+    _want(logits, "logits", torch.float32)
+    _want(out, "out", torch.float32, (n, rows))
+    _want(a_log, "a_log", torch.float32, (rows // max(per_head, 1),))
+    _want(dt_bias, "dt_bias", torch.float32, (rows,))
+    _check(library().ms_low_rank_expand(_ptr(logits), _i(ld), _i(col), _i(rows), None, _i(rows), _i(1), _ptr(a_log), _ptr(dt_bias),
+                                        _i(per_head), _ptr(out), _i(0), _i(n), _stream()))
+
+
+def low_rank_expand(mid: torch.Tensor, col: int, weight: torch.Tensor, out: torch.Tensor, a_log: Optional[torch.Tensor] = None,
+                    bias: Optional[torch.Tensor] = None, per_head: int = 0) -> None:
+    """The second product of a projection made in two steps: ``value[n, r] = sum_j mid[n, col + j] weight[r, j]`` with ``mid``
+    float32 ``[N, ld]`` and ``weight`` float32 ``[R, rank]``.  Without ``a_log``: ``out [N, R]`` (any type) receives the values.
+    With ``a_log`` (float32 ``[R / per_head]``) and ``bias`` (float32 ``[R]``): ``out`` float32 receives the decays
+    ``exp(-exp(a_log[r // per_head]) softplus(value + bias[r]))``."""
+    n, ld = mid.shape
+    rows, rank = weight.shape
+    _want(mid, "mid", torch.float32)
+    _want(weight, "weight", torch.float32)
+    decay = a_log is not None
+    if decay:
+        _want(a_log, "a_log", torch.float32, (rows // max(per_head, 1),))
+        _want(bias, "bias", torch.float32, (rows,))
+    _want(out, "out", torch.float32 if decay else None, (n, rows))
+    _check(library().ms_low_rank_expand(_ptr(mid), _i(ld), _i(col), _i(rank), _ptr(weight), _i(rows), _i(1 if decay else 0),
+                                        _ptr(a_log), _ptr(bias), _i(per_head), _ptr(out), _i(_code(out.dtype)), _i(n), _stream()))
 
 
 def head_norm_gate(y: torch.Tensor, bottom: Optional[torch.Tensor], weight: torch.Tensor, gate: torch.Tensor, gate_col: int,

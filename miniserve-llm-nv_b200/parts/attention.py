@@ -25,6 +25,15 @@ projected, before their norm and rotation).  With any of them the projections (q
 logits) are one product over a row-concatenated weight padded with zero rows to a multiple of eight, followed by
 ``kernels.qkv_prepare`` (per-head norm, rotation, append) and ``kernels.paged_attention`` with the sink and the gate
 applied as it stores.
+
+More options of the general form: ``bias`` (the q, k, v and output projections have biases, ``<name><bias_suffix>``; those of
+q, k and v are added in float32 as ``kernels.qkv_prepare`` reads the heads), ``qk_norm_weight=False`` (the per-head norm of q
+and k has no weight: ``x / rms(x)``; such a norm commutes with the rotation, which turns pairs of entries and leaves a head's
+root mean square as it is, so it covers designs that norm after rotating), ``output_gate="entry"`` (the concatenated heads
+are multiplied entry by entry by ``sigmoid(W_g x)``, a gate of ``num_heads * value_dim`` rows, before the output projection) and
+``conv_taps`` (q, k and v pass a short causal convolution per channel, ``<name><conv_suffix>`` of shape ``[channels, taps]``
+without bias, directly after the projection; the last ``taps - 1`` projected rows are the request's state, so
+``cache_need()`` is then the pair (pages, state)).
 """
 
 from __future__ import annotations
@@ -34,7 +43,7 @@ from typing import Optional, Sequence, Union
 import torch
 
 from .. import kernels
-from .base import POSITIONS, FoldedInput, NormFold, PagedKVNeed, ParamSpec, Part, ResidualAdd, register_mixer
+from .base import POSITIONS, FoldedInput, NormFold, PagedKVNeed, ParamSpec, Part, ResidualAdd, StateNeed, register_mixer
 from .context import PagedKVView, StepContext
 from .spec import PartSpec
 
@@ -49,10 +58,12 @@ class Attention(Part):
                  v_name: str = "v_proj.weight", o_name: str = "o_proj.weight", q_norm_name: str = "q_norm.weight",
                  k_norm_name: str = "k_norm.weight", value_dim: Optional[int] = None, sink: bool = False,
                  output_gate: bool = False, own_kv: bool = True, gate_name: str = "g_proj.weight",
-                 values_from_keys: bool = False) -> None:
+                 values_from_keys: bool = False, bias: bool = False, bias_suffix: str = ".b", qk_norm_weight: bool = True,
+                 conv_taps: Optional[int] = None, conv_suffix: str = ".conv") -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
-        general_form = bool(sink or output_gate or not own_kv or values_from_keys or (value_dim is not None and value_dim != head_dim))
+        general_form = bool(sink or output_gate or not own_kv or values_from_keys or (value_dim is not None and value_dim != head_dim)
+                            or bias or conv_taps or not qk_norm_weight)
         if general_form and 1 <= head_dim <= kernels.MAX_HEAD_DIM:
             pass            # (the general form's kernels take odd head sizes too; the rotation checks its own size)
         elif head_dim % 2 or not 2 <= head_dim <= kernels.MAX_HEAD_DIM:
@@ -74,17 +85,28 @@ class Attention(Part):
         self.value_dim = head_dim if value_dim is None else int(value_dim)
         if not 1 <= self.value_dim <= kernels.MAX_HEAD_DIM:
             raise ValueError(f"value head size {self.value_dim} is not in 1..{kernels.MAX_HEAD_DIM}")
+        if output_gate not in (False, True, "head", "entry"):
+            raise ValueError(f"output_gate is False, 'head' (True) or 'entry', not {output_gate!r}")
         self.sink, self.output_gate, self.own_kv = bool(sink), bool(output_gate), bool(own_kv)
+        self.gate_per_entry = output_gate == "entry"
+        self.bias, self.qk_norm_weight = bool(bias), bool(qk_norm_weight)
+        self.conv_taps = int(conv_taps) if conv_taps else None
+        if self.conv_taps is not None and (not own_kv or values_from_keys or not 1 <= self.conv_taps <= kernels.MAX_CONV_TAPS):
+            raise ValueError(f"conv_taps {conv_taps}: 1..{kernels.MAX_CONV_TAPS} taps on a layer's own queries, keys and values")
         # the general form: one product for all projections of the input, then qkv_prepare and the general call of
         # paged_attention (the fast paths below are written for plain heads of one size)
         self.values_from_keys = bool(values_from_keys)
         if self.values_from_keys and (self.value_dim != head_dim or not self.own_kv):
             raise ValueError("values_from_keys: the values are the layer's own keys, so both have the same size")
-        self.general = self.sink or self.output_gate or not self.own_kv or self.values_from_keys or self.value_dim != head_dim
+        self.general = (self.sink or self.output_gate or not self.own_kv or self.values_from_keys or self.value_dim != head_dim
+                        or self.bias or self.conv_taps is not None or not self.qk_norm_weight)
         if self.general and (self.score_softcap or self.score_bias_slopes is not None):
             raise ValueError("score modifiers are not implemented together with value_dim, sink, output_gate or own_kv=False")
         self.names = dict(q=prefix + q_name, k=prefix + k_name, v=prefix + v_name, o=prefix + o_name,
                           q_norm=prefix + q_norm_name, k_norm=prefix + k_norm_name, g=prefix + gate_name)
+        for key in ("q", "k", "v", "o"):
+            self.names[key + "_b"] = self.names[key] + bias_suffix
+            self.names[key + "_conv"] = self.names[key] + conv_suffix
         # columns of the general form's projection: queries, keys, values, gate logits, zero padding
         q_rows = num_heads * head_dim
         kv_rows = num_kv_heads * (head_dim + (0 if self.values_from_keys else self.value_dim)) if self.own_kv else 0
@@ -93,7 +115,10 @@ class Attention(Part):
         if self.values_from_keys:
             self.v_col = self.k_col            # the value columns ARE the key columns, read before norm and rotation
         self.gate_col = q_rows + kv_rows if self.output_gate else -1
-        self.in_rows = (q_rows + kv_rows + (num_heads if self.output_gate else 0) + 7) // 8 * 8
+        self.gate_rows = 0 if not self.output_gate else num_heads * self.value_dim if self.gate_per_entry else num_heads
+        self.in_rows = (q_rows + kv_rows + self.gate_rows + 7) // 8 * 8
+        self.conv_channels = q_rows + kv_rows          # (queries, keys and values are the projection's first columns)
+        self.in_bias = self.o_bias = self.conv_weight = None
         self.qkv_weight: Optional[torch.Tensor] = None
         self.o_weight: Optional[torch.Tensor] = None
         self.q_norm_weight: Optional[torch.Tensor] = None
@@ -107,17 +132,32 @@ class Attention(Part):
             specs.append(ParamSpec(self.names["k"], (self.num_kv_heads * d, h)))
             if not self.values_from_keys:
                 specs.append(ParamSpec(self.names["v"], (self.num_kv_heads * dv, h)))
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weight:
             specs.append(ParamSpec(self.names["q_norm"], (d,), "vector"))
             if self.own_kv:
                 specs.append(ParamSpec(self.names["k_norm"], (d,), "vector"))
         if self.output_gate:
-            specs.append(ParamSpec(self.names["g"], (self.num_heads, h)))
+            specs.append(ParamSpec(self.names["g"], (self.gate_rows, h)))
         specs.append(ParamSpec(self.names["o"], (h, self.num_heads * dv)))
+        present = ["q"] + (["k"] if self.own_kv else []) + (["v"] if self.own_kv and not self.values_from_keys else [])
+        if self.bias:
+            specs += [ParamSpec(self.names[key + "_b"], (self._rows_of(key),), "vector") for key in present + ["o"]]
+        if self.conv_taps is not None:
+            specs += [ParamSpec(self.names[key + "_conv"], (self._rows_of(key), self.conv_taps)) for key in present]
         return specs
 
-    def cache_need(self) -> PagedKVNeed:
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window, None if self.value_dim == self.head_dim else self.value_dim)
+    def _rows_of(self, key: str) -> int:
+        return {"q": self.num_heads * self.head_dim, "k": self.num_kv_heads * self.head_dim,
+                "v": self.num_kv_heads * self.value_dim, "o": self.hidden_size}[key]
+
+    def cache_need(self):
+        pages = PagedKVNeed(self.num_kv_heads, self.head_dim, self.window, None if self.value_dim == self.head_dim else self.value_dim)
+        if self.conv_taps is None:
+            return pages
+        return (pages, StateNeed(((self.conv_taps - 1) * self.conv_channels,), torch.float32))
+
+    def cache_members(self) -> list:
+        return [self, self]
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
@@ -132,9 +172,24 @@ class Attention(Part):
             if padding:
                 pieces.append(torch.zeros((padding, self.hidden_size), dtype=pieces[0].dtype, device=pieces[0].device))
             self.qkv_weight = torch.cat(pieces, dim=0).contiguous()
-            if self.qk_norm:
+            if self.qk_norm and self.qk_norm_weight:
                 self.q_norm_weight = tensors[n["q_norm"]].float().contiguous()
                 self.k_norm_weight = tensors[n["k_norm"]].float().contiguous() if self.own_kv else None
+            elif self.qk_norm:
+                self.q_norm_weight = torch.ones(self.head_dim, dtype=torch.float32, device=self.o_weight.device)
+                self.k_norm_weight = self.q_norm_weight if self.own_kv else None
+            present = ["q"] + (["k"] if self.own_kv else []) + (["v"] if self.own_kv and not self.values_from_keys else [])
+            if self.bias:
+                self.in_bias = torch.zeros(self.in_rows, dtype=torch.float32, device=self.o_weight.device)
+                at = 0
+                for key in present:
+                    self.in_bias[at:at + self._rows_of(key)] = tensors[n[key + "_b"]].float()
+                    at += self._rows_of(key)
+                self.o_bias = tensors[n["o_b"]].float().contiguous()
+            if self.conv_taps is not None:
+                self.conv_weight = torch.cat([tensors[n[key + "_conv"]].float() for key in present], dim=0).contiguous()
+                if self.in_bias is not None:
+                    self.in_bias = self.in_bias[:self.conv_channels].contiguous()      # (the convolution adds it to its inputs)
             return
         self.qkv_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
         if self.qk_norm:
@@ -202,26 +257,41 @@ class Attention(Part):
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
         return out
 
-    def _forward_general(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
-        """The form with a sink, a gate, value heads of their own size or another run's keys and values."""
+    def _forward_general(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        """The form with a sink, a gate, value heads of their own size, another run's keys and values, biases or a
+        convolution on the projections."""
         n, d, dv = x.shape[0], self.head_dim, self.value_dim
         n_q, n_kv = self.num_heads, self.num_kv_heads
+        state = None
+        if self.conv_taps is not None:
+            cache, state = cache
         if cache.writable != self.own_kv:
             raise RuntimeError("a layer with keys and values of its own writes its cache; a layer without reads another run's")
         proj = ctx.buffer("attention.proj", (n, self.in_rows), x.dtype)
         kernels.linear(x, self.qkv_weight, proj)
+        heads = proj
+        if state is not None:
+            # queries, keys and values are the first columns: the convolution keeps their places
+            heads = ctx.buffer("attention.conv", (n, self.conv_channels), x.dtype)
+            kernels.causal_conv(proj, 0, self.conv_weight, None, state.states, 0, ctx.state_slots, ctx.query_start,
+                                ctx.max_query_len, heads, activation="none", in_bias=self.in_bias)
         cos_sin, rotary_dim, interleaved = self.position.fused_args(ctx)
         q = ctx.buffer("attention.q", (n, n_q, d), x.dtype)
-        kernels.qkv_prepare(proj, 0, self.k_col, self.v_col, n_q, n_kv, d, dv, cache.slots, self.q_norm_weight,
+        kernels.qkv_prepare(heads, 0, self.k_col, self.v_col, n_q, n_kv, d, dv, cache.slots, self.q_norm_weight,
                             self.k_norm_weight, self.eps, cos_sin, rotary_dim, cache.key_pool, cache.value_pool, q,
-                            interleaved=interleaved)
+                            interleaved=interleaved, bias=self.in_bias if state is None else None)
         attended = ctx.buffer("attention.attended", (n, n_q, dv), x.dtype)
+        per_head = self.output_gate and not self.gate_per_entry
         kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
                                 ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
                                 ctx.max_context_len, self.scale, self.window, attended, ctx.host_query_start or None,
-                                sink=self.sink, gate=proj if self.output_gate else None, gate_col=max(self.gate_col, 0))
+                                sink=self.sink, gate=proj if per_head else None, gate_col=max(self.gate_col, 0))
+        if self.gate_per_entry:
+            kernels.sigmoid_gate_mul(attended.view(n, n_q * dv), proj, self.gate_col, attended.view(n, n_q * dv))
         out = ctx.buffer("attention.out", (n, self.hidden_size), x.dtype)
         kernels.linear(attended.view(n, n_q * dv), self.o_weight, out)
+        if self.o_bias is not None:
+            kernels.add_bias(out, self.o_bias)
         return out
 
     def _attend(self, q: torch.Tensor, ctx: StepContext, cache: PagedKVView, attended: torch.Tensor) -> None:

@@ -16,6 +16,8 @@ mixer           ``forward(x, ctx, cache) -> y``; ``cache_need()`` says what ``ca
                 mixer made of several: ``cache`` is then the tuple of their views)
 feed_forward    ``forward(x, ctx) -> y``
 block           ``forward(residual, delta, ctx, cache) -> delta``: arranges the four above
+embedding       ``add(residual, ctx, cache)``: adds rows of a table of its own to the token embeddings in the
+                float32 stream; ``cache_need()`` as for a mixer (a state that a sequence carries, or None)
 ==============  ==========================================================================
 
 A new part is a class registered under a name with ``register_norm`` / ``register_position``
@@ -56,16 +58,32 @@ class ParamSpec:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """The mixer keeps keys and values per token in pages; ``window`` keys back at most (None: all).  ``value_dim``:
-    the size of a value head where it differs from the size of a key head (None: the same)."""
+    the size of a value head where it differs from the size of a key head (None: the same).  ``chunk``: a token sees only
+    the keys of its own chunk of that many positions, counted from position 0 (None: no chunks)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
     @property
     def value_head_dim(self) -> int:
         return self.head_dim if self.value_dim is None else self.value_dim
+
+    @property
+    def keeps_all(self) -> bool:
+        """Whether every key stays visible to later tokens (no window passes it, no chunk ends)."""
+        return self.window is None and self.chunk is None
+
+    def first_needed(self, position: int) -> int:
+        """The first key that a query at ``position`` or later can still see."""
+        first = 0
+        if self.window is not None:
+            first = max(first, position - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, position - position % self.chunk)
+        return first
 
 
 @dataclass(frozen=True)
@@ -76,6 +94,13 @@ class PagedLatentNeed:
     rank: int
     rot: int
     window: Optional[int] = None
+
+    @property
+    def keeps_all(self) -> bool:
+        return self.window is None
+
+    def first_needed(self, position: int) -> int:
+        return 0 if self.window is None else max(0, position - self.window + 1)
 
 
 PAGED_NEEDS = (PagedKVNeed, PagedLatentNeed)     # needs whose cache is paged: block tables, slots, pages given back
@@ -124,6 +149,16 @@ class PostNormed:
 
 
 @dataclass
+class ChannelScaled:
+    """What a block hands on where a sublayer's output is multiplied channel by channel before it is added to the stream
+    (a layer scale, with any constant of the design folded into ``weight``): the stream receives ``weight * x``, formed and
+    added in float32 by the norm that reads the stream next (``kernels.postnorm_add_rmsnorm`` without its division)."""
+
+    x: torch.Tensor
+    weight: torch.Tensor
+
+
+@dataclass
 class FoldedInput:
     """What a part receives as ``x`` where the norm before it was folded: ``x = residual * norm weight`` and the
     statistics that its first product completes the norm with (``kernels.RowStats``)."""
@@ -165,12 +200,14 @@ class Registry:
 
 
 NORMS = Registry("norm")
+EMBEDDINGS = Registry("embedding")
 POSITIONS = Registry("position")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed_forward")
 BLOCKS = Registry("block")
 
 register_norm = NORMS.register
+register_embedding = EMBEDDINGS.register
 register_position = POSITIONS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register

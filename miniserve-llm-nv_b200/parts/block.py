@@ -2,6 +2,8 @@
 (miniserve/model/qwen3.py:336-346).  ``parallel``: one norm whose output both sublayers read,
 ``h += mixer(norm(h)) + feed_forward(norm(h))``; a layer without a feed-forward is ``h += mixer(norm(h))``.
 ``sandwich``: a norm on both sides of each sublayer, ``h += post(mixer(norm(h))); h += post(feed_forward(norm(h)))``.
+``scaled_pre_norm``: ``pre_norm`` where what a sublayer adds is multiplied by a constant and, channel by channel, by a vector
+of the layer (a layer scale): ``h += m * s1 * mixer(norm(h)); h += m * s2 * feed_forward(norm(h))``.
 
 The residual stream ``h`` is float32 and is updated in place.  A block receives the stream
 together with a *pending* ``delta`` that has not been added yet (the previous block's
@@ -23,11 +25,11 @@ from typing import Any, Optional, Union
 import torch
 
 from .. import kernels
-from .base import FoldedInput, NormFold, PostNormed, ResidualAdd, register_block
+from .base import ChannelScaled, FoldedInput, NormFold, ParamSpec, Part, PostNormed, ResidualAdd, register_block
 from .context import StepContext
 
 # what a block hands on: nothing, an output still to add (or two, whose float32 sum is to be added), or a folded input
-Pending = Union[None, torch.Tensor, tuple, FoldedInput, PostNormed]
+Pending = Union[None, torch.Tensor, tuple, FoldedInput, PostNormed, ChannelScaled]
 
 
 def fold_between(producer, norm, consumer, ctx: StepContext) -> Optional[tuple]:
@@ -158,3 +160,53 @@ class SandwichBlock:
         normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)      # (the mixer has read the first)
         self.feed_forward_norm.add_and_norm(residual, mixed, normed)
         return PostNormed(self.feed_forward.forward(normed, ctx), *self.feed_forward_post_norm.fold(), self.residual_scale)
+
+
+class LayerScales(Part):
+    """The vectors that multiply a layer's sublayer outputs channel by channel, kept in float32 with the design's
+    constant folded in."""
+
+    def __init__(self, names: list, size: int, constant: float) -> None:
+        self.names, self.size, self.constant = list(names), size, float(constant)
+        self.weights: dict = {}
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(name, (self.size,), "vector") for name in self.names]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weights = {name: (tensors[name].float() * self.constant).contiguous() for name in self.names}
+
+
+@register_block("scaled_pre_norm")
+class ScaledPreNormBlock:
+    """``x <- x + m * s1 * mixer(norm_1(x))``, then ``x <- x + m * s2 * feed_forward(norm_2(x))`` with a constant ``m``
+    (``residual_scale``) and the layer's vectors ``s1``, ``s2`` (``mixer_scale_name``, ``feed_forward_scale_name``: full tensor
+    names).  A layer may have no feed-forward.  A sublayer's output is handed on unadded with its vector
+    (:class:`~.base.ChannelScaled`); the norm that reads the stream next multiplies, adds in float32 and norms in one kernel.
+    """
+
+    def __init__(self, *, mixer, feed_forward, mixer_norm, feed_forward_norm, hidden_size: int, mixer_scale_name: str,
+                 feed_forward_scale_name: Optional[str] = None, residual_scale: float = 1.0) -> None:
+        if (feed_forward is None) != (feed_forward_norm is None) or (feed_forward is None) != (feed_forward_scale_name is None):
+            raise ValueError("a scaled pre-norm block has a feed-forward with its norm and its scale, or none of the three")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.mixer_scale_name, self.feed_forward_scale_name = mixer_scale_name, feed_forward_scale_name
+        names = [mixer_scale_name] + ([] if feed_forward_scale_name is None else [feed_forward_scale_name])
+        self.scales = LayerScales(names, hidden_size, residual_scale)
+
+    def parts(self):
+        every = (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.scales)
+        return [part for part in every if part is not None]
+
+    def forward(self, residual: torch.Tensor, pending: Pending, ctx: StepContext, cache: Any) -> Pending:
+        if isinstance(pending, FoldedInput):
+            raise TypeError("a scaled pre-norm block takes its input from its own norm")
+        normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)
+        self.mixer_norm.add_and_norm(residual, pending, normed)
+        mixed = ChannelScaled(self.mixer.forward(normed, ctx, cache), self.scales.weights[self.mixer_scale_name])
+        if self.feed_forward is None:
+            return mixed
+        normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)      # (the mixer has read the first)
+        self.feed_forward_norm.add_and_norm(residual, mixed, normed)
+        return ChannelScaled(self.feed_forward.forward(normed, ctx), self.scales.weights[self.feed_forward_scale_name])

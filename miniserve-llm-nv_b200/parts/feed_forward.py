@@ -4,7 +4,8 @@ matrix product over one weight that holds both.  Where the intermediate size is 
 the rows of the two alternate in blocks of eight (``kernels.interleave_gate_up``), which lets the
 product of a decode step apply the activation as it stores; else the up rows follow the gate rows.  With ``bias=True`` the
 three projections have biases (``down(act(gate(x) + b_g) * (up(x) + b_u)) + b_d``, added in float32 as the activation and
-the output are formed); the up rows then follow the gate rows."""
+the output are formed); the up rows then follow the gate rows.  ``mlp``: ``down(act(up(x)))`` without a gate and without biases,
+``act`` the square of ReLU."""
 
 from __future__ import annotations
 
@@ -97,4 +98,32 @@ class GatedMLP(Part):
                 kernels.add_bias(out, self.down_bias)
             else:
                 kernels.gated_linear(gate_up, self.down_weight, out)
+        return out
+
+
+@register_feed_forward("mlp")
+class PlainMLP(Part):
+    def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "relu_square",
+                 up_name: str = "up", down_name: str = "down") -> None:
+        if activation != "relu_square":
+            raise ValueError(f"mlp implements the 'relu_square' activation, not {activation!r}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.names = dict(up=prefix + up_name, down=prefix + down_name)
+        self.up_weight: Optional[torch.Tensor] = None
+        self.down_weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(self.names["up"], (self.intermediate_size, self.hidden_size)),
+                ParamSpec(self.names["down"], (self.hidden_size, self.intermediate_size))]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.up_weight, self.down_weight = tensors[self.names["up"]], tensors[self.names["down"]]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n = x.shape[0]
+        hidden = ctx.buffer("mlp.hidden", (n, self.intermediate_size), x.dtype)
+        kernels.linear(x, self.up_weight, hidden)
+        kernels.relu_square(hidden)
+        out = ctx.buffer("mlp.out", (n, self.hidden_size), x.dtype)
+        kernels.linear(hidden, self.down_weight, out)
         return out

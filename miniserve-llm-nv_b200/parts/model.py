@@ -13,7 +13,7 @@ from typing import Any, Optional, Union
 import torch
 
 from .. import kernels
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PagedKVNeed, PagedLatentNeed, ParamSpec, StateNeed
+from .base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, PagedKVNeed, PagedLatentNeed, ParamSpec, StateNeed
 from .context import StepContext
 from .spec import ModelSpec
 
@@ -49,17 +49,19 @@ class DecoderModel:
             self.blocks.append(BLOCKS.build(layer.block, mixer=mixer, feed_forward=feed_forward,
                                             mixer_norm=mixer_norm, feed_forward_norm=feed_forward_norm, **post))
         self.final_norm = NORMS.build(spec.final_norm)
+        self.extra_embeddings = [EMBEDDINGS.build(part) for part in spec.extra_embeddings]
         for index, run in enumerate(spec.order):
             if not 0 <= run.layer < len(self.blocks):
                 raise ValueError(f"order[{index}] names layer {run.layer}, the model has {len(self.blocks)}")
             if run.cache_of is not None and not 0 <= run.cache_of < index:
                 raise ValueError(f"order[{index}] reads the cache of entry {run.cache_of}, which does not come before it")
-        self.cache_groups, self.run_caches = self._plan_caches()
+        self.cache_groups, self.run_caches, self.embedding_caches = self._plan_caches()
         self.embedding: Optional[torch.Tensor] = None
         self.output_weight: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ description
     def parts(self):
+        yield from self.extra_embeddings
         for block in self.blocks:
             yield from block.parts()
         yield self.final_norm
@@ -73,10 +75,26 @@ class DecoderModel:
             specs.append(ParamSpec(spec.output_name, (spec.vocab_size, spec.hidden_size)))
         return specs
 
-    def _plan_caches(self) -> tuple[list[CacheGroup], list[Optional[RunCache]]]:
+    def _plan_caches(self) -> tuple[list[CacheGroup], list, list]:
+        """Cache groups, the plan of every run's cache (None, a :class:`RunCache`, or a tuple of these, nested as the
+        mixer's ``cache_need()`` is) and the plans of the extra embeddings' states."""
         keys: list[Any] = []
         counts: list[int] = []
-        runs: list[Optional[RunCache]] = []
+
+        def own(need):
+            """A cache of its own for ``need`` (a tuple: for every member; None: nothing)."""
+            if need is None:
+                return None
+            if isinstance(need, tuple):
+                return tuple(own(member) for member in need)
+            if need not in keys:
+                keys.append(need)
+                counts.append(0)
+            group = keys.index(need)
+            counts[group] += 1
+            return RunCache(group, counts[group] - 1, writable=True)
+
+        runs: list = []
         for index, run in enumerate(self.spec.order):
             mixer = self.blocks[run.layer].mixer
             need = mixer.cache_need() if hasattr(mixer, "cache_need") else None
@@ -84,21 +102,10 @@ class DecoderModel:
                 runs.append(None)
                 continue
             if isinstance(need, tuple):
-                # a mixer made of several (side by side): a cache of its own for every member that needs one
+                # a mixer made of several (side by side, or one around another): a cache of its own for every member that needs one
                 if run.cache_of is not None:
                     raise ValueError(f"order[{index}]: a mixer of several members cannot read another run's cache")
-                plans = []
-                for member in need:
-                    if member is None:
-                        plans.append(None)
-                        continue
-                    if member not in keys:
-                        keys.append(member)
-                        counts.append(0)
-                    group = keys.index(member)
-                    plans.append(RunCache(group, counts[group], writable=True))
-                    counts[group] += 1
-                runs.append(tuple(plans))
+                runs.append(own(need))
                 continue
             if run.cache_of is not None:
                 source = runs[run.cache_of]
@@ -106,13 +113,9 @@ class DecoderModel:
                     raise ValueError(f"order[{index}] cannot read the cache of entry {run.cache_of}: forms differ")
                 runs.append(RunCache(source.group, source.slot, writable=False))
                 continue
-            if need not in keys:
-                keys.append(need)
-                counts.append(0)
-            group = keys.index(need)
-            runs.append(RunCache(group, counts[group], writable=True))
-            counts[group] += 1
-        return [CacheGroup(need, count) for need, count in zip(keys, counts)], runs
+            runs.append(own(need))
+        embeddings = [own(part.cache_need() if hasattr(part, "cache_need") else None) for part in self.extra_embeddings]
+        return [CacheGroup(need, count) for need, count in zip(keys, counts)], runs, embeddings
 
     @staticmethod
     def cache_groups_need(keys, group):
@@ -131,6 +134,8 @@ class DecoderModel:
         spec = self.spec
         residual = torch.empty((ctx.n_tokens, spec.hidden_size), dtype=torch.float32, device=self.device)
         kernels.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
+        for part, plan in zip(self.extra_embeddings, self.embedding_caches):
+            part.add(residual, ctx, None if plan is None else storage.run_view(plan, ctx))
         delta = None            # what a block hands to the next: see parts.block
         for index, run in enumerate(spec.order):
             plan = self.run_caches[index]

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from .base import ParamSpec, Part, PostNormed, register_norm
+from .base import ChannelScaled, ParamSpec, Part, PostNormed, register_norm
 
 
 @register_norm("rms")
@@ -42,6 +42,10 @@ class RMSNorm(Part):
             # the output of the sublayer before passes its own norm on the way into the stream: one kernel for both
             kernels.postnorm_add_rmsnorm(residual, delta.x, delta.weight, delta.eps, self.weight, self.eps, out, rows,
                                          post_scale=delta.scale)
+            return out
+        if isinstance(delta, ChannelScaled):
+            # the output of the sublayer before is multiplied channel by channel (in float32) on its way into the stream
+            kernels.postnorm_add_rmsnorm(residual, delta.x, delta.weight, 0.0, self.weight, self.eps, out, rows, post_norm=False)
             return out
         second = None
         if isinstance(delta, tuple):

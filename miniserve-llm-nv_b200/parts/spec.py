@@ -74,3 +74,6 @@ class ModelSpec:
     embedding_scale: float = 1.0
     logit_scale: float = 1.0
     logit_softcap: Optional[float] = None
+    # Parts of the embedding family whose rows are added to the (scaled) token embeddings, each with a table of its own
+    # and, where it looks back along the sequence, a state that the request carries.
+    extra_embeddings: Sequence[PartSpec] = ()

@@ -72,6 +72,21 @@ def weight_files(folder: Path) -> list[Path]:
     return files
 
 
+def stored_shapes(folder: Union[str, Path]) -> dict[str, tuple[int, ...]]:
+    """``{name: shape}`` of every tensor in the folder's safetensors files, read from their headers alone."""
+    import struct
+
+    shapes: dict[str, tuple[int, ...]] = {}
+    for path in weight_files(Path(folder)):
+        with open(path, "rb") as handle:
+            (length,) = struct.unpack("<Q", handle.read(8))
+            header = json.loads(handle.read(length))
+        for name, entry in header.items():
+            if name != "__metadata__":
+                shapes[name] = tuple(int(v) for v in entry["shape"])
+    return shapes
+
+
 def kept_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
     if spec.kind == "table":
         return torch.int32

@@ -142,7 +142,7 @@ def linear_add(x, weight, residual):
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
                     max_query_len, max_context_len, scale, window, out, host_query_start=None, softcap=None,
-                    bias_slopes=None, sink=False, gate=None, gate_col=0):
+                    bias_slopes=None, sink=False, gate=None, gate_col=0, chunk=None):
     n, n_q, d = q.shape
     n_kv, page_size = k_pool.shape[1], k_pool.shape[2]
     group = n_q // n_kv
@@ -150,6 +150,8 @@ def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions
         pos = int(positions[token])
         table = block_tables[int(request_of_token[token])]
         first = max(0, pos - window + 1) if window else 0
+        if chunk:
+            first = max(first, pos - pos % chunk)
         keys = torch.arange(first, pos + 1)
         pages = table[(keys // page_size).long()].long()
         offsets = (keys % page_size).long()
@@ -346,11 +348,13 @@ def relu_square(x):
 # --------------------------------------------------------------------------- norms on both sides, free projection layouts
 
 
-def postnorm_add_rmsnorm(residual, delta, post_weight, post_eps, weight, eps, out, rows=None, post_scale=1.0):
+def postnorm_add_rmsnorm(residual, delta, post_weight, post_eps, weight, eps, out, rows=None, post_scale=1.0, post_norm=True):
     add = 0.0
     if delta is not None:
         d = delta.double()
-        add = post_scale * post_weight.double() * (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps))
+        if post_norm:
+            d = d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps)
+        add = post_scale * post_weight.double() * d
     if rows is None:
         if delta is not None:
             residual += add.to(residual.dtype)
@@ -363,8 +367,10 @@ def postnorm_add_rmsnorm(residual, delta, post_weight, post_eps, weight, eps, ou
 
 
 def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots, q_weight, k_weight, eps, cos_sin,
-                rotary_dim, k_pool, v_pool, q_out, interleaved=False):
+                rotary_dim, k_pool, v_pool, q_out, interleaved=False, bias=None, value_heads=None):
     n = proj.shape[0]
+    if bias is not None:
+        proj = proj.double() + bias.double()
 
     def heads(col, count, size, weight):
         x = proj[:, col:col + count * size].double().view(n, count, size)
@@ -378,14 +384,15 @@ def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots
     if k_col < 0:
         return
     k = heads(k_col, n_kv, head_dim, k_weight)
-    v = proj[:, v_col:v_col + n_kv * value_dim].view(n, n_kv, value_dim)
+    value_heads = n_kv if value_heads is None else value_heads
+    v = proj[:, v_col:v_col + value_heads * value_dim].view(n, value_heads, value_dim).repeat(1, n_kv // value_heads, 1)
     page_size = k_pool.shape[2]
     for token in range(n):
         slot = int(slots[token])
         if slot < 0:
             continue
         k_pool[slot // page_size, :, slot % page_size, :] = k[token].to(k_pool.dtype)
-        v_pool[slot // page_size, :, slot % page_size, :] = v[token]
+        v_pool[slot // page_size, :, slot % page_size, :] = v[token].to(v_pool.dtype)
 
 
 # --------------------------------------------------------------------------- state-space mixer
@@ -489,8 +496,12 @@ def decay_gates(logits, a_log, dt_bias, gates):
 
 
 def matrix_scan(mode, q, q_col, k, k_col, v, v_col, gates, states, state_offset, state_slots, query_start, max_query_len, heads,
-                kv_heads, dim, vdim, y, q_scale=1.0, bottom=None):
+                kv_heads, dim, vdim, y, q_scale=1.0, bottom=None, gate_col=0, channel_decay=None, input_activation="none"):
     per = heads // kv_heads
+
+    def act(x):
+        return x * torch.sigmoid(x) if input_activation == "silu" else x
+
     columns = vdim + 1 if mode == "memory" else vdim
     for r in range(state_slots.numel()):
         lo, hi = int(query_start[r]), int(query_start[r + 1])
@@ -499,9 +510,20 @@ def matrix_scan(mode, q, q_col, k, k_col, v, v_col, gates, states, state_offset,
         kept = states[int(state_slots[r]), state_offset:state_offset + heads * columns * dim].view(heads, columns, dim)
         S = kept.double().clone()                # [head, column, dim]: column c of the matrix, the last one n
         for t in range(lo, hi):
-            qt = (q_scale * q[t, q_col:q_col + kv_heads * dim].double()).view(kv_heads, dim).repeat_interleave(per, dim=0)
-            kt = k[t, k_col:k_col + kv_heads * dim].double().view(kv_heads, dim).repeat_interleave(per, dim=0)
-            vt = v[t, v_col:v_col + heads * vdim].double().view(heads, vdim)
+            qt = (q_scale * act(q[t, q_col:q_col + kv_heads * dim].double())).view(kv_heads, dim).repeat_interleave(per, dim=0)
+            kt = act(k[t, k_col:k_col + kv_heads * dim].double()).view(kv_heads, dim).repeat_interleave(per, dim=0)
+            vt = act(v[t, v_col:v_col + heads * vdim].double()).view(heads, vdim)
+            if mode == "decay":
+                S = gates.double()[:, None, None] * S + vt[:, :, None] * kt[:, None, :]
+                y[t] = torch.einsum("hcd,hd->hc", S, qt).to(y.dtype)
+                continue
+            if mode == "channel_delta":
+                beta = torch.sigmoid(gates[t, gate_col:gate_col + heads].double())
+                S = channel_decay[t].double().view(heads, 1, dim) * S
+                u = beta[:, None] * (vt - torch.einsum("hcd,hd->hc", S, kt))
+                S = S + u[:, :, None] * kt[:, None, :]
+                y[t] = torch.einsum("hcd,hd->hc", S, qt).to(y.dtype)
+                continue
             g = gates[t].double()
             if mode == "memory":
                 vt = torch.cat([vt, torch.ones(heads, 1, dtype=torch.float64)], dim=1)
@@ -555,6 +577,76 @@ def gated_recurrence_scan(u, pre, gate_bias, rate, proj, y_col, y_bias, states, 
         kept.copy_(S.to(kept.dtype))
 
 
+# --------------------------------------------------------------------------- one token back, pairs of outputs, two score maps
+
+
+def softplus(x):
+    return torch.clamp(x, min=0.0) + torch.log1p(torch.exp(-x.abs()))
+
+
+def low_rank_expand(mid, col, weight, out, a_log=None, bias=None, per_head=0):
+    rank = weight.shape[1]
+    value = mid[:, col:col + rank].double() @ weight.double().T
+    if a_log is not None:
+        value = torch.exp(-torch.exp(a_log.double()).repeat_interleave(per_head) * softplus(value + bias.double()))
+    out.copy_(value.to(out.dtype))
+
+
+def channel_decays(logits, col, a_log, dt_bias, per_head, out):
+    rows = out.shape[1]
+    value = logits[:, col:col + rows].double()
+    out.copy_(torch.exp(-torch.exp(a_log.double()).repeat_interleave(per_head) * softplus(value + dt_bias.double())).to(out.dtype))
+
+
+def normed_sum(a, a_weight, a_scale, b, b_weight, b_scale, eps, out):
+    def normed(x, w):
+        x = x.double()
+        return w.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))
+    out.copy_((a_scale * normed(a, a_weight) + b_scale * normed(b, b_weight)).to(out.dtype))
+
+
+def sigmoid_gate_mul(x, gate, gate_col, out):
+    width = x.shape[1]
+    out.copy_((x.double() * torch.sigmoid(gate[:, gate_col:gate_col + width].double())).to(out.dtype))
+
+
+def differential_combine(a, lam, eps, out_scale, gate, gate_col, out):
+    n, both, dv = a.shape
+    heads = both // 2
+    o = a[:, :heads].double() - lam * a[:, heads:].double()
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+    if gate is not None:
+        o = o * torch.sigmoid(gate[:, gate_col:gate_col + heads * dv].double()).view(n, heads, dv)
+    out.copy_(o.to(out.dtype))
+
+
+def token_shift(x, shift, states, state_offset, state_slots, query_start, request_of_token, out):
+    hidden = x.shape[1]
+    for r in range(state_slots.numel()):
+        lo, hi = int(query_start[r]), int(query_start[r + 1])
+        if hi == lo:
+            continue
+        kept = states[int(state_slots[r]), state_offset:state_offset + hidden]
+        before = torch.cat([kept.double()[None, :], x[lo:hi - 1].double()], dim=0)
+        now = x[lo:hi].double()
+        kept.copy_(x[hi - 1].to(kept.dtype))
+        out[lo:hi] = (now + (before - now) * shift.double()).to(out.dtype)
+
+
+def pair_embedding(tokens, table, buckets, mul_prev, mul_cur, states, state_slots, query_start, request_of_token, residual):
+    for r in range(state_slots.numel()):
+        lo, hi = int(query_start[r]), int(query_start[r + 1])
+        if hi == lo:
+            continue
+        before = int(states[int(state_slots[r]), 0]) - 1
+        for t in range(lo, hi):
+            token = int(tokens[t])
+            row = buckets if before < 0 else (before * mul_prev + token * mul_cur) % buckets
+            residual[t] += table[row].to(residual.dtype)
+            before = token
+        states[int(state_slots[r]), 0] = before + 1
+
+
 def install(monkeypatch) -> None:
     """Puts the functions above in place of the kernel bindings (CPU tests of host logic only)."""
     import miniserve_b200  # noqa: F401
@@ -565,7 +657,9 @@ def install(monkeypatch) -> None:
                  "latent_attention", "head_gate", "linear_batched", "router_topk", "expert_route", "expert_linear",
                  "expert_combine", "relu_square", "clamped_glu", "postnorm_add_rmsnorm", "qkv_prepare", "causal_conv_silu",
                  "selective_scan", "gated_group_norm", "causal_conv", "add_bias", "scaled_sum", "small_linear_f32",
-                 "unit_norm_heads", "exponential_gates", "decay_gates", "matrix_scan", "head_norm_gate", "gated_recurrence_scan"):
+                 "unit_norm_heads", "exponential_gates", "decay_gates", "matrix_scan", "head_norm_gate", "gated_recurrence_scan",
+                 "low_rank_expand", "channel_decays", "normed_sum", "sigmoid_gate_mul", "differential_combine", "token_shift",
+                 "pair_embedding"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
     monkeypatch.setattr(kernels, "latent_attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
