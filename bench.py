@@ -519,6 +519,28 @@ def _kivurax(width, memory, delta, left, right, dense_ff, experts, top, expert_f
     return dict(architecture="Kivurax", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, layers=entries)
 
 
+def _bafavik(width, left, linear, differential, delta, ff, vocab):
+    """Four layers: softmax attention beside linear attention, differential attention under a chunked mask, convolved softmax
+    attention beside the channel delta rule, softmax attention beside linear attention; a squared-ReLU feed-forward each."""
+    heads, kv_heads, dim, vdim = left
+    attention = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=dim ** -0.5, rot=dict(base=1000000.0, dims=dim // 2))
+    l_heads, l_dim, l_vdim = linear
+    decays = [1.0 - 2.0 ** (-1 - 8 * h / l_heads) for h in range(l_heads)]
+    pair = dict(type="parallel", mixer=dict(left=attention, right=dict(heads=l_heads, dim=l_dim, vdim=l_vdim, decay=decays),
+                                            left_scale=1.0, right_scale=1.0))
+    d_heads, d_kv, d_dim, d_vdim, chunk = differential
+    diff = dict(type="attention", mixer=dict(heads=d_heads, kv_heads=d_kv, dim=d_dim, vdim=d_vdim, scale=d_dim ** -0.5, diff=0.5,
+                                             mask=dict(size=chunk)))
+    r_heads, r_kv, r_dim, r_vdim, rank = delta
+    pair_2 = dict(type="parallel_2", mixer=dict(
+        left=dict(attention, conv=4),
+        right=dict(heads=r_heads, kv_heads=r_kv, dim=r_dim, vdim=r_vdim, conv=4, decay_rank=rank, gate_rank=rank)))
+    mlp = dict(kind="dense", ff=ff)
+    return dict(architecture="Bafavik", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, logit_scale=1.0,
+                embedding=dict(scale=1.0, bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=7919)), loop=None,
+                layers=[dict(pair, mlp=mlp), dict(diff, mlp=mlp), dict(pair_2, mlp=mlp), dict(pair, mlp=mlp)])
+
+
 # Layer sizes that resemble real models' (random weights, four layers each: two with a gated MLP, two with experts), and
 # the Qwen3 layers of equal width, head count and inner size beside them.
 DESIGN_SIZES = {
@@ -547,11 +569,23 @@ DESIGN_SIZES = {
     "recurrent-lite": dict(kivurax=_kivurax(2048, (16, 64, 128), (32, 16, 64, 64), (32, 8, 64, 512), (2560, 20), 10944, 60, 6, 1408, 32000),
                            zozezen=_zozezen(2048, 32, 8, 64, 32, 128, 64, 4, 60, 4, 6, 1408, 2816, 32000),
                            qwen3=dict(hidden_size=2048, intermediate_size=10944, num_attention_heads=32, num_key_value_heads=8, head_dim=64)),
+    # Bafavik: sixteen heads of 128 over four key heads beside a linear attention of sixteen heads of 128; differential attention
+    # of sixteen heads (two maps of 64, values of 128) over four key heads in chunks of 1,024; the same softmax attention behind
+    # convolutions beside a delta rule of sixteen value heads of 128 over eight query/key heads with two-step projections through
+    # 64 numbers; feed-forward 6,144; beside it Kivurax (the closest design: side-by-side mixers, the delta rule, recurrent and
+    # attention layers) and Qwen3 at the same width
+    "pairs-small": dict(bafavik=_bafavik(2048, (16, 4, 128, 128), (16, 128, 128), (16, 4, 64, 128, 1024), (16, 8, 128, 128, 64), 6144, 32000),
+                        kivurax=_kivurax(2048, (8, 128, 256), (16, 8, 128, 128), (16, 4, 128, 1024), (2048, 16), 6144, 16, 4, 1024, 32000),
+                        qwen3=dict(hidden_size=2048, intermediate_size=6144, num_attention_heads=16, num_key_value_heads=4, head_dim=128)),
+    # the same with heads of 64 everywhere, chunks of 512, feed-forward 10,944
+    "pairs-lite": dict(bafavik=_bafavik(2048, (32, 8, 64, 64), (32, 64, 64), (32, 8, 64, 64, 512), (32, 16, 64, 64, 32), 10944, 32000),
+                       kivurax=_kivurax(2048, (16, 64, 128), (32, 16, 64, 64), (32, 8, 64, 512), (2560, 20), 10944, 60, 6, 1408, 32000),
+                       qwen3=dict(hidden_size=2048, intermediate_size=10944, num_attention_heads=32, num_key_value_heads=8, head_dim=64)),
 }
 
 
 def designs_workload(args) -> int:
-    """``--workload designs``: prompt and decode throughput of Vesidra, Zozezen and Kivurax at sizes that resemble real models' layers, beside
+    """``--workload designs``: prompt and decode throughput of Vesidra, Zozezen, Kivurax and Bafavik at sizes that resemble real models' layers, beside
     the Qwen3 decoder at equal width, depth, head count and inner size; one JSON line per size and design, with each
     step's kernels (device time by kernel, from the framework profiler) so that like kernels can be set side by side."""
     import torch
@@ -702,7 +736,7 @@ def main() -> int:
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--workload", choices=("default", "mixed", "sweep", "designs"), default="default",
-                        help="designs: Vesidra, Zozezen and Kivurax beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
+                        help="designs: Vesidra, Zozezen, Kivurax and Bafavik beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="with --workload designs: one size only")
     parser.add_argument("--sweep-prompt", type=int, default=1024)
     parser.add_argument("--sweep-new", type=int, default=128)
