@@ -385,10 +385,12 @@ __global__ void sigmoid_gate_mul_kernel(const T* __restrict__ x, const T* __rest
 
 // One warp per (token, head): o = first - lambda second with first = a[n, head], second = a[n, heads + head] (the outputs of
 // two score maps over the same values), o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate[n, gate_col + head dv + c]).
+// `wide`: dv is a multiple of four, at most 512, and every row lies on a boundary of four numbers: a lane keeps its pieces of
+// four in registers between the sum and the output.
 template <typename T>
 __global__ void differential_combine_kernel(const T* __restrict__ a, int heads, int dv, float lambda, float eps,
                                             float out_scale, const T* __restrict__ gate, int gate_ld, int gate_col,
-                                            T* __restrict__ out, long long items) {
+                                            T* __restrict__ out, long long items, int wide) {
   grid_dependency_wait();
   grid_dependency_launch();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -398,14 +400,50 @@ __global__ void differential_combine_kernel(const T* __restrict__ a, int heads, 
   const int head = (int)(item % heads);
   const T* first = a + (n * 2 * heads + head) * dv;
   const T* second = a + (n * 2 * heads + heads + head) * dv;
+  const T* g = gate ? gate + n * gate_ld + gate_col + (size_t)head * dv : nullptr;
+  T* dst = out + (n * heads + head) * dv;
+  if (wide) {
+    constexpr int PIECES = 4;
+    const int pieces = dv >> 2;
+    float o[PIECES][4];
+    Quad<T> gates[PIECES];
+    float sum_sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+      const int at = lane + 32 * j;
+      if (at < pieces) {
+        const Quad<T> x = reinterpret_cast<const Quad<T>*>(first)[at], y = reinterpret_cast<const Quad<T>*>(second)[at];
+        if (g) gates[j] = reinterpret_cast<const Quad<T>*>(g)[at];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o[j][e] = to_float(x.v[e]) - lambda * to_float(y.v[e]);
+          sum_sq += o[j][e] * o[j][e];
+        }
+      }
+    }
+    const float inv = out_scale / sqrtf(warp_sum(sum_sq) / (float)dv + eps);
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+      const int at = lane + 32 * j;
+      if (at < pieces) {
+        Quad<T> result;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = o[j][e] * inv;
+          if (g) v /= 1.f + expf(-to_float(gates[j].v[e]));
+          result.v[e] = from_float<T>(v);
+        }
+        reinterpret_cast<Quad<T>*>(dst)[at] = result;
+      }
+    }
+    return;
+  }
   float sum_sq = 0.f;
   for (int c = lane; c < dv; c += 32) {
     const float o = to_float(first[c]) - lambda * to_float(second[c]);
     sum_sq += o * o;
   }
   const float inv = out_scale / sqrtf(warp_sum(sum_sq) / (float)dv + eps);
-  const T* g = gate ? gate + n * gate_ld + gate_col + (size_t)head * dv : nullptr;
-  T* dst = out + (n * heads + head) * dv;
   for (int c = lane; c < dv; c += 32) {
     float o = (to_float(first[c]) - lambda * to_float(second[c])) * inv;
     if (g) o /= 1.f + expf(-to_float(g[c]));
@@ -448,8 +486,11 @@ MS_EXPORT int ms_differential_combine(const void* a, int heads, int dv, float la
   if (items == 0 || dv == 0) return 0;
   const long long blocks = (items + 3) / 4;
   MS_REQUIRE(blocks < 2147483647LL, "differential_combine: %lld heads in one launch is too many", items);
+  const size_t four = dtype == MS_F32 ? 16 : 8;
+  const int wide = dv % 4 == 0 && dv <= 512 && reinterpret_cast<size_t>(a) % four == 0 && reinterpret_cast<size_t>(out) % four == 0 &&
+                   (gate == nullptr || (reinterpret_cast<size_t>(gate) % four == 0 && gate_ld % 4 == 0 && gate_col % 4 == 0));
   MS_EG_DISPATCH(dtype, (ms::launch(differential_combine_kernel<T>, (unsigned)blocks, 128, 0, stream, (const T*)a, heads, dv, lambda,
-                                    eps, out_scale, (const T*)gate, gate_ld, gate_col, (T*)out, items)));
+                                    eps, out_scale, (const T*)gate, gate_ld, gate_col, (T*)out, items, wide)));
   MS_CHECK_LAUNCH("differential_combine");
   return 0;
 }

@@ -344,6 +344,45 @@ __global__ void low_rank_expand_kernel(const float* __restrict__ mid, int ld, in
   out[i] = from_float<T>(sum);
 }
 
+// The same product for many results: a block of 256 threads owns 256 results (consecutive r) of kExpandTokens tokens.  The
+// tokens' `rank` numbers lie in shared memory (every thread reads the same one at a time), the second matrix is given
+// TRANSPOSED, wt [rank, rows], so that the threads of a warp read consecutive numbers, and each of its numbers feeds
+// kExpandTokens multiply-adds.  A result's sum runs over j in ascending order whatever the tile.
+constexpr int kExpandTokens = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+low_rank_expand_tiled_kernel(const float* __restrict__ mid, int ld, int col, int rank, const float* __restrict__ wt, int rows,
+                             int decay, const float* __restrict__ a_log, const float* __restrict__ bias, int per_head,
+                             T* __restrict__ out, int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  extern __shared__ float expand_smem[];                      // [kExpandTokens][rank]
+  const int t0 = blockIdx.y * kExpandTokens;
+  const int len = min(kExpandTokens, n_tokens - t0);
+  for (int i = threadIdx.x; i < kExpandTokens * rank; i += blockDim.x) {
+    const int t = i / rank, j = i % rank;
+    expand_smem[i] = t < len ? mid[(size_t)(t0 + t) * ld + col + j] : 0.f;
+  }
+  __syncthreads();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float acc[kExpandTokens];
+#pragma unroll
+  for (int t = 0; t < kExpandTokens; ++t) acc[t] = 0.f;
+  for (int j = 0; j < rank; ++j) {
+    const float w = wt[(size_t)j * rows + r];
+#pragma unroll
+    for (int t = 0; t < kExpandTokens; ++t) acc[t] += expand_smem[t * rank + j] * w;
+  }
+  float rate = 0.f, b = 0.f;
+  if (decay) rate = -expf(a_log[r / per_head]), b = bias[r];
+#pragma unroll
+  for (int t = 0; t < kExpandTokens; ++t) {
+    if (t < len) out[(size_t)(t0 + t) * rows + r] = from_float<T>(decay ? expf(rate * softplus_f(acc[t] + b)) : acc[t]);
+  }
+}
+
 // One warp per (token, head): v = y / bottom, v / sqrt(mean(v^2) + eps) * weight * act(gate).  Where a head's row is
 // at most 512 numbers, a multiple of four, and lies on 16-byte boundaries in all four arrays (`wide`), a lane keeps its
 // four-number pieces in registers between the sum and the output and every access is one piece; otherwise number by number.
@@ -412,6 +451,37 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ y, const float* 
       const float factor = activation ? g * sigmoid_f(g) : sigmoid_f(g);
       dst[c] = from_float<T>((row[c] / divisor) * inv * w[c] * factor);
     }
+  }
+}
+
+// The same for long rows (all heads normed together: one "head" of thousands of numbers): a block of 256 threads a (token,
+// head), the sum of squares over the block in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_gate_block_kernel(const float* __restrict__ y, const float* __restrict__ bottom, const float* __restrict__ weight,
+                            int weight_per_head, const T* __restrict__ gate, int gate_ld, int gate_col, int activation, float eps,
+                            T* __restrict__ out, int heads, int vdim) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float scratch[32];
+  const long long item = blockIdx.x;
+  const size_t token = (size_t)(item / heads);
+  const int head = (int)(item % heads);
+  const float* row = y + (size_t)item * vdim;
+  const float divisor = bottom ? bottom[item] : 1.f;
+  const float* w = weight + (weight_per_head ? (size_t)head * vdim : 0);
+  const T* z = gate + token * gate_ld + gate_col + (size_t)head * vdim;
+  T* dst = out + (token * heads + head) * vdim;
+  float sum_sq = 0.f;
+  for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+    const float value = row[c] / divisor;
+    sum_sq += value * value;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)vdim + eps);
+  for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+    const float g = to_float(z[c]);
+    const float factor = activation ? g * sigmoid_f(g) : sigmoid_f(g);
+    dst[c] = from_float<T>((row[c] / divisor) * inv * w[c] * factor);
   }
 }
 
@@ -624,21 +694,32 @@ MS_EXPORT int ms_matrix_scan(int mode, const void* q, int q_ld, int q_col, const
   return 0;
 }
 
-// mid float32 rows of ld numbers (the first product's results from column col); w float32 [rows, rank]; out [tokens, rows] of
-// type `dtype`, or, decay != 0, float32 decays exp(-exp(a_log[row / per_head]) softplus(. + bias[row])).  w null (rank == rows):
-// the numbers of mid themselves take the place of the product.
-MS_EXPORT int ms_low_rank_expand(const float* mid, int ld, int col, int rank, const float* w, int rows, int decay,
+// mid float32 rows of ld numbers (the first product's results from column col); wt float32 [rank, rows], the second matrix
+// TRANSPOSED; out [tokens, rows] of type `dtype`, or, decay != 0, float32 decays exp(-exp(a_log[row / per_head]) softplus(. +
+// bias[row])).  wt null (rank == rows): the numbers of mid themselves take the place of the product.
+MS_EXPORT int ms_low_rank_expand(const float* mid, int ld, int col, int rank, const float* wt, int rows, int decay,
                                  const float* a_log, const float* bias, int per_head, void* out, int dtype, int n_tokens,
                                  cudaStream_t stream) {
   const long long total = (long long)n_tokens * rows;
   if (total == 0) return 0;
   MS_REQUIRE(rank >= 1 && col >= 0 && col + rank <= ld, "low_rank_expand: %d numbers from column %d of rows of %d", rank, col, ld);
-  MS_REQUIRE(w != nullptr || rank == rows, "low_rank_expand: without a second matrix the %d numbers are the %d results", rank, rows);
+  MS_REQUIRE(wt != nullptr || rank == rows, "low_rank_expand: without a second matrix the %d numbers are the %d results", rank, rows);
   MS_REQUIRE(!decay || (a_log && bias && per_head >= 1 && rows % per_head == 0 && dtype == MS_F32),
              "low_rank_expand: decays are float32 and need A_log, a bias and the heads' size (%d rows, %d a head)", rows, per_head);
+  if (wt != nullptr) {
+    const size_t smem = (size_t)kExpandTokens * rank * sizeof(float);
+    MS_REQUIRE(smem <= 48 * 1024, "low_rank_expand: %d numbers a token do not fit the shared memory", rank);
+    const int token_tiles = (n_tokens + kExpandTokens - 1) / kExpandTokens;
+    MS_REQUIRE(token_tiles <= 65535, "low_rank_expand: %d tokens in one launch is too many", n_tokens);
+    dim3 grid((rows + 255) / 256, token_tiles);
+    MS_REC_DISPATCH(dtype, (ms::launch(low_rank_expand_tiled_kernel<T>, grid, 256, smem, stream, mid, ld, col, rank, wt, rows, decay,
+                                       a_log, bias, per_head, (T*)out, n_tokens)));
+    MS_CHECK_LAUNCH("low_rank_expand");
+    return 0;
+  }
   const long long blocks = (total + 255) / 256;
   MS_REQUIRE(blocks < 2147483647LL, "low_rank_expand: %lld numbers in one launch is too many", total);
-  MS_REC_DISPATCH(dtype, (ms::launch(low_rank_expand_kernel<T>, (unsigned)blocks, 256, 0, stream, mid, ld, col, rank, w, rows, decay,
+  MS_REC_DISPATCH(dtype, (ms::launch(low_rank_expand_kernel<T>, (unsigned)blocks, 256, 0, stream, mid, ld, col, rank, wt, rows, decay,
                                      a_log, bias, per_head, (T*)out, total)));
   MS_CHECK_LAUNCH("low_rank_expand");
   return 0;
@@ -651,6 +732,14 @@ MS_EXPORT int ms_head_norm_gate(const float* y, const float* bottom, const float
                                 int heads, int vdim, cudaStream_t stream) {
   if (n_tokens == 0 || heads == 0 || vdim == 0) return 0;
   MS_REQUIRE(activation == 0 || activation == 1, "head_norm_gate: activation code %d", activation);
+  if (vdim > 128 * kHeadPieces) {
+    const long long rows_ = (long long)n_tokens * heads;
+    MS_REQUIRE(rows_ < 2147483647LL, "head_norm_gate: %lld rows in one launch is too many", rows_);
+    MS_REC_DISPATCH(dtype, (ms::launch(head_norm_gate_block_kernel<T>, (unsigned)rows_, 256, 0, stream, y, bottom, weight, weight_per_head,
+                                       (const T*)gate, gate_ld, gate_col, activation, eps, (T*)out, heads, vdim)));
+    MS_CHECK_LAUNCH("head_norm_gate");
+    return 0;
+  }
   // blocks of eight warps that walk the (token, head) pairs with the grid's stride: at most sixteen blocks a multiprocessor
   const int warps = 8;
   long long blocks = ((long long)n_tokens * heads + warps - 1) / warps;

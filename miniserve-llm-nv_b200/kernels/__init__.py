@@ -978,22 +978,23 @@ def channel_decays(logits: torch.Tensor, col: int, a_log: torch.Tensor, dt_bias:
                                         _i(per_head), _ptr(out), _i(0), _i(n), _stream()))
 
 
-def low_rank_expand(mid: torch.Tensor, col: int, weight: torch.Tensor, out: torch.Tensor, a_log: Optional[torch.Tensor] = None,
+def low_rank_expand(mid: torch.Tensor, col: int, weight_t: torch.Tensor, out: torch.Tensor, a_log: Optional[torch.Tensor] = None,
                     bias: Optional[torch.Tensor] = None, per_head: int = 0) -> None:
-    """The second product of a projection made in two steps: ``value[n, r] = sum_j mid[n, col + j] weight[r, j]`` with ``mid``
-    float32 ``[N, ld]`` and ``weight`` float32 ``[R, rank]``.  Without ``a_log``: ``out [N, R]`` (any type) receives the values.
+    """The second product of a projection made in two steps: ``value[n, r] = sum_j mid[n, col + j] weight_t[j, r]`` with ``mid``
+    float32 ``[N, ld]`` and ``weight_t`` float32 ``[rank, R]``, the second matrix TRANSPOSED (the kernel's threads then read
+    consecutive numbers).  Without ``a_log``: ``out [N, R]`` (any type) receives the values.
     With ``a_log`` (float32 ``[R / per_head]``) and ``bias`` (float32 ``[R]``): ``out`` float32 receives the decays
     ``exp(-exp(a_log[r // per_head]) softplus(value + bias[r]))``."""
     n, ld = mid.shape
-    rows, rank = weight.shape
+    rank, rows = weight_t.shape
     _want(mid, "mid", torch.float32)
-    _want(weight, "weight", torch.float32)
+    _want(weight_t, "weight_t", torch.float32)
     decay = a_log is not None
     if decay:
         _want(a_log, "a_log", torch.float32, (rows // max(per_head, 1),))
         _want(bias, "bias", torch.float32, (rows,))
     _want(out, "out", torch.float32 if decay else None, (n, rows))
-    _check(library().ms_low_rank_expand(_ptr(mid), _i(ld), _i(col), _i(rank), _ptr(weight), _i(rows), _i(1 if decay else 0),
+    _check(library().ms_low_rank_expand(_ptr(mid), _i(ld), _i(col), _i(rank), _ptr(weight_t), _i(rows), _i(1 if decay else 0),
                                         _ptr(a_log), _ptr(bias), _i(per_head), _ptr(out), _i(_code(out.dtype)), _i(n), _stream()))
 
 

@@ -186,9 +186,9 @@ class DeltaRule(Part):
         small = [tensors[n["b"]].float(), tensors[n["a"] if self.decay_rank is None else n["a1"]].float()]
         if self.gate_rank is not None:
             small.append(tensors[n["g1"]].float())
-            self.gate_expand = tensors[n["g2"]].float().contiguous()
+            self.gate_expand = tensors[n["g2"]].float().t().contiguous()          # [rank, H * dv]: the kernel reads it transposed
         if self.decay_rank is not None:
-            self.decay_expand = tensors[n["a2"]].float().contiguous()
+            self.decay_expand = tensors[n["a2"]].float().t().contiguous()
         self.gate_weight = torch.cat(small, dim=0).contiguous()
         self.a_log = tensors[n["a_log"]].float().contiguous()
         self.dt_bias = tensors[n["dt_bias"]].float().contiguous()

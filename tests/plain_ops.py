@@ -584,9 +584,9 @@ def softplus(x):
     return torch.clamp(x, min=0.0) + torch.log1p(torch.exp(-x.abs()))
 
 
-def low_rank_expand(mid, col, weight, out, a_log=None, bias=None, per_head=0):
-    rank = weight.shape[1]
-    value = mid[:, col:col + rank].double() @ weight.double().T
+def low_rank_expand(mid, col, weight_t, out, a_log=None, bias=None, per_head=0):
+    rank = weight_t.shape[0]
+    value = mid[:, col:col + rank].double() @ weight_t.double()
     if a_log is not None:
         value = torch.exp(-torch.exp(a_log.double()).repeat_interleave(per_head) * softplus(value + bias.double()))
     out.copy_(value.to(out.dtype))

@@ -149,19 +149,19 @@ def test_differential_combine_kernel(dtype, heads, dv, gated):
     assert not torch.allclose(other, want, atol=0.05)
 
 
-@pytest.mark.parametrize("heads,dim,rank,rows_out", [(4, 12, 5, 35), (1, 10, 1, 14), (6, 64, 24, 192)])
+@pytest.mark.parametrize("heads,dim,rank,rows_out", [(4, 12, 5, 35), (1, 10, 1, 14), (6, 64, 24, 192), (16, 128, 64, 2048)])
 def test_two_step_projection_kernels(heads, dim, rank, rows_out):
     from miniserve_b200 import kernels
 
     n = 11
     mid = rand((n, 3 + rank + 2), torch.float32, 1)
-    second, a_log, bias = rand((heads * dim, rank), torch.float32, 2, 0.5), rand((heads,), torch.float32, 3, 0.3) - 2.0, rand((heads * dim,), torch.float32, 4, 0.5)
+    second, a_log, bias = rand((rank, heads * dim), torch.float32, 2, 0.5), rand((heads,), torch.float32, 3, 0.3) - 2.0, rand((heads * dim,), torch.float32, 4, 0.5)
     decays, want = torch.empty((n, heads * dim)).cuda(), torch.empty((n, heads * dim), dtype=torch.float64)
     kernels.low_rank_expand(mid, 3, second, decays, a_log, bias, dim)
     plain_ops.low_rank_expand(cpu(mid), 3, cpu(second), want, cpu(a_log), cpu(bias), dim)
     assert torch.allclose(cpu(decays).double(), want, atol=1e-6) and 0 < float(want.min()) and float(want.max()) < 1
     for dtype in DTYPES:
-        gate_weight = rand((rows_out, rank), torch.float32, 5, 0.5)
+        gate_weight = rand((rank, rows_out), torch.float32, 5, 0.5)
         gate, want_gate = torch.empty((n, rows_out), dtype=dtype).cuda(), torch.empty((n, rows_out), dtype=torch.float64)
         kernels.low_rank_expand(mid, 3, gate_weight, gate)
         plain_ops.low_rank_expand(cpu(mid), 3, cpu(gate_weight), want_gate)
@@ -170,6 +170,27 @@ def test_two_step_projection_kernels(heads, dim, rank, rows_out):
     kernels.channel_decays(logits, 2, a_log, bias, dim, decays)
     plain_ops.channel_decays(cpu(logits), 2, cpu(a_log), cpu(bias), dim, want)
     assert torch.allclose(cpu(decays).double(), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,vdim", [(1, 2048), (1, 600), (2, 516), (4, 20)])
+def test_head_norm_over_long_rows_and_squared_relu(dtype, heads, vdim):
+    """All heads normed together are one long row (a block a row); the squared ReLU in pieces of sixteen bytes and number by
+    number."""
+    from miniserve_b200 import kernels
+
+    n = 7
+    y, weight = rand((n, heads, vdim), torch.float32, 1, 2.0), 1 + rand((heads * vdim,), torch.float32, 2, 0.2)
+    gate = rand((n, heads * vdim + 8), dtype, 3, 2.0)
+    out, want = torch.empty((n, heads * vdim), dtype=dtype).cuda(), torch.empty((n, heads * vdim), dtype=torch.float64)
+    kernels.head_norm_gate(y, None, weight, gate, 8, "sigmoid", 1e-5, out)
+    plain_ops.head_norm_gate(cpu(y), None, cpu(weight), cpu(gate), 8, "sigmoid", 1e-5, want)
+    assert close(out, want, dtype)
+    for shape in ((n, heads * vdim), (3, 43)):
+        x = rand(shape, dtype, 4, 2.0)
+        expected = cpu(x).double().clamp(min=0).pow(2)
+        kernels.relu_square(x)
+        assert close(x, expected, dtype)
 
 
 SCAN_SIZES = [(4, 2, 12, 20), (1, 1, 10, 14), (2, 2, 128, 64), (3, 1, 9, 5), (6, 6, 64, 32), (2, 1, 200, 8)]
