@@ -55,16 +55,17 @@ def close(got, expected, dtype=torch.float32, scale=None):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [12, 96, 1000])
-def test_token_shift_kernel(dtype, hidden):
+@pytest.mark.parametrize("hidden,offset", [(12, 7), (96, 7), (96, 8), (1000, 16), (2048, 0)])
+def test_token_shift_kernel(dtype, hidden, offset):
     """Unequal requests (one of a single token) in slots out of order, from states that are not zero at an offset of the
-    slots' rows; then the same tokens in two steps give the same bits as in one."""
+    slots' rows (on a 16-byte boundary, where the kernel moves pieces of eight numbers, and off it); then the same tokens in
+    two steps give the same bits as in one."""
     from miniserve_b200 import kernels
 
-    lengths, slots, offset = [5, 1, 33, 2], [3, 0, 4, 1], 7
+    lengths, slots = [5, 1, 33, 2], [3, 0, 4, 1]
     n = sum(lengths)
     x, shift = rand((n, hidden), dtype, 1), torch.rand(hidden, generator=torch.Generator().manual_seed(2)).cuda()
-    states = rand((6, offset + hidden + 3), torch.float32, 3)
+    states = rand((6, offset + hidden + 4), torch.float32, 3)
     before = cpu(states)
     out = torch.empty_like(x)
     kernels.token_shift(x, shift, states, offset, ints(slots), starts_of(lengths), requests_of(lengths), out)
