@@ -139,15 +139,16 @@ MS_EXPORT int ms_token_shift(const void* x, int dtype, const float* shift, float
 
 // tokens int32 [n_tokens]; table [buckets + 1, hidden] of type `dtype`; states int32 rows of state_stride numbers; residual
 // float32 [n_tokens, hidden], added to.
-MS_EXPORT int ms_pair_embedding(const int* tokens, const void* table, int dtype, int buckets, int mul_prev, int mul_cur,
+MS_EXPORT int ms_pair_embedding(const int* tokens, const void* table, int dtype, int buckets, long long mul_prev, long long mul_cur,
                                 int* states, long long state_stride, int state_offset, const int* state_slots,
                                 const int* query_start, const int* request_of_token, float* residual, int n_tokens, int hidden,
                                 cudaStream_t stream) {
   if (n_tokens == 0 || hidden == 0) return 0;
-  MS_REQUIRE(buckets >= 1 && mul_prev >= 0 && mul_cur >= 0, "pair_embedding: %d buckets, factors %d and %d", buckets, mul_prev, mul_cur);
+  MS_REQUIRE(buckets >= 1 && mul_prev >= 0 && mul_cur >= 0 && mul_prev < (1LL << 31) && mul_cur < (1LL << 31),
+             "pair_embedding: %d buckets, factors %lld and %lld (0 .. 2^31 - 1: the hash is formed in 64 bits)", buckets, mul_prev, mul_cur);
   const int threads = hidden >= 1024 ? 256 : 128;
   MS_SEQ_DISPATCH(dtype, (ms::launch(pair_embedding_kernel<T>, n_tokens, threads, 0, stream, tokens, (const T*)table, buckets,
-                                     (long long)mul_prev, (long long)mul_cur, states, state_stride, state_offset, state_slots,
+                                     mul_prev, mul_cur, states, state_stride, state_offset, state_slots,
                                      query_start, request_of_token, residual, hidden)));
   MS_CHECK_LAUNCH("pair_embedding");
   return 0;

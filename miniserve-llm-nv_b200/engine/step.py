@@ -62,7 +62,8 @@ class DecodeGraph:
         self.copied: Optional[torch.cuda.Event] = None     # recorded after the last copy of the host mirror
         # per row: (the request's cache record, pages of its committed table that the mirror shows, per group)
         self.row_owner: list = [None] * rows
-        self.has_windows = any(not need.keeps_all for need in manager.paged_needs)
+        # groups whose pages can be given back behind a window or a chunk: a row's table may change anywhere between two steps
+        self.gives_back = [not need.keeps_all for need in manager.paged_needs]
         self.meta = torch.zeros(self.offsets[-1], dtype=torch.int32, device=sf.device)
         self.n_groups = n_groups
         self.scratch = storage.scratch_page
@@ -303,17 +304,29 @@ class StepFunction:
             # The row keeps what it shows only for the very same admission (a request id can come back after a
             # release, with other pages), and only as far as the pages were committed when they were written:
             # a page reserved for a step that was aborted may be another one next time.
-            same = owner is not None and owner[0] is record and not graph.has_windows
+            same = owner is not None and owner[0] is record
+            released_now = []
             for g in range(graph.n_groups):
                 table = item.tables[g]
                 if len(table) > graph.width:
                     raise ValueError("a block table is wider than the model's longest context")
+                base = o[8 + 2 * g] + row * graph.width
                 # committed pages that this row already shows stay; the others are checked and written
                 first = owner[1][g] if same and owner[1][g] <= len(table) else 0
+                released = 0
+                if graph.gives_back[g]:
+                    # a group behind a window or a chunk: the pages wholly before the first key that the request's next
+                    # token can see went back at the last commit; the row shows the scratch page in their places
+                    released = min(manager.paged_needs[g].first_needed(item.start) // ps, len(table))
+                    if first > 0 and owner[2][g] <= released:
+                        if released > owner[2][g]:
+                            host[base + owner[2][g]:base + released] = scratch
+                    else:
+                        first = 0
+                released_now.append(released)
                 fresh = table[first:]
                 if any(p != RELEASED and not 0 <= p < limit for p in fresh):
                     raise ValueError("a page lies outside the pool")
-                base = o[8 + 2 * g] + row * graph.width
                 if fresh:
                     host[base + first:base + len(table)] = [scratch if p == RELEASED else p for p in fresh]
                 if first == 0:
@@ -322,7 +335,7 @@ class StepFunction:
                 if not 0 <= slot < limit * ps:
                     raise ValueError(f"slot {slot} outside the pool")
                 host[o[9 + 2 * g] + row] = slot
-            graph.row_owner[row] = (record, [len(item.tables[g]) - len(item.new_pages[g]) for g in range(graph.n_groups)])
+            graph.row_owner[row] = (record, [len(item.tables[g]) - len(item.new_pages[g]) for g in range(graph.n_groups)], released_now)
         host[o[0]:o[0] + n] = tokens
         host[o[1]:o[1] + n] = positions
         host[o[4]:o[4] + n] = lens
