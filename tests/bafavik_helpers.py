@@ -80,6 +80,42 @@ BAFAVIK_D = model(120, 44, 1e-5, 0.8, 1.3, 0.5, (11, 3, 2), (1, 2, 4), [
 CONFIGS = {"a": BAFAVIK_A, "b": BAFAVIK_B, "c": BAFAVIK_C, "d": BAFAVIK_D}
 
 
+def random_config(rng) -> dict:
+    """A configuration drawn from ``rng`` (a ``random.Random``): one to five layers of any kind in any order, head counts,
+    head sizes, taps, chunks, inner sizes of the two-step projections and a repeated run drawn independently of one another."""
+    width = rng.choice([24, 40, 64, 72])
+
+    def left(conv):
+        kv = rng.choice([1, 2, 3])
+        dim = rng.choice([4, 6, 8, 10, 16])
+        dims = rng.choice([0, 2, dim // 2 * 2, dim // 4 * 2])
+        return softmax_left(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([4, 8, 12]), rng.uniform(0.1, 0.5),
+                            rot(rng.choice([100.0, 10000.0]), dims), conv=rng.choice([1, 2, 3, 4, 6]) if conv else None)
+
+    layers = []
+    for _ in range(rng.choice([1, 2, 3, 4, 5])):
+        kind, ff = rng.choice(["parallel", "attention", "parallel_2"]), rng.choice([None, 16, 24, 50])
+        if kind == "parallel":
+            heads = rng.choice([1, 2, 3, 5])
+            layers.append(layer(pair(left(False), heads, rng.choice([4, 6, 9, 16]), rng.choice([4, 8, 10]),
+                                     [rng.uniform(0.5, 0.999) for _ in range(heads)], rng.uniform(0.3, 1.5), rng.uniform(0.3, 1.5)), ff))
+        elif kind == "attention":
+            kv = rng.choice([1, 2])
+            layers.append(layer(differential(kv * rng.choice([1, 2, 3]), kv, rng.choice([4, 6, 16]), rng.choice([4, 5, 16]),
+                                             rng.uniform(0.1, 0.5), rng.uniform(0.1, 0.9), rng.choice([1, 2, 5, 8, 16, 33, 500])), ff))
+        else:
+            kv = rng.choice([1, 2])
+            layers.append(layer(pair_2(left(True), kv * rng.choice([1, 2, 3]), kv, rng.choice([4, 6, 9, 16]), rng.choice([8, 10]),
+                                       rng.choice([1, 2, 4, 5]), rng.choice([1, 3, 8]), rng.choice([1, 2, 7])), ff))
+    loop = None
+    if rng.random() < 0.7:
+        start = rng.randrange(0, len(layers))
+        loop = (start, rng.randrange(start + 1, len(layers) + 1), rng.choice([1, 2, 3]))
+    bigram = (rng.choice([7, 97, 1021]), rng.choice([1, 31, 99991]), rng.choice([1, 7, 5003])) if rng.random() < 0.8 else None
+    return model(rng.choice([50, 131]), width, rng.choice([1e-5, 1e-6]), rng.uniform(0.3, 1.2), rng.uniform(0.3, 1.5),
+                 rng.uniform(0.5, 3.0), bigram, loop, layers)
+
+
 def _normal(shape, seed, std, mean=0.0):
     return mean + std * torch.randn(shape, generator=torch.Generator().manual_seed(seed))
 

@@ -218,6 +218,38 @@ def test_cuttings_match_plain_on_cpu(cpu_runtime, name, page_size, cutting):
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_on_cpu(cpu_runtime, tmp_path, seed):
+    """Layer kinds, orders, head counts, sizes, taps, chunks and repeated runs drawn at random, in a cutting and with a page
+    size drawn with them."""
+    import random
+
+    from miniserve_b200.trace import TraceSession
+
+    rng = random.Random(seed)
+    config = bh.random_config(rng)
+    bh.CONFIGS[f"random{seed}"] = config
+    try:
+        page_size = rng.choice([4, 8, 16])
+        requests = {f"r{i}": helpers.random_tokens(config["vocab"], n, seed=20 + i) for i, n in enumerate((1, 6, 17, 30, 41))}
+        cutting = rng.choice(["tail", "portions", "mixed"])
+        steps = {"tail": lambda r: helpers.cut_decode_tail(r, 9), "portions": helpers.cut_portions, "mixed": helpers.cut_mixed}[cutting](requests)
+        pages = (helpers.max_live_tokens(steps, granule=page_size * 2) + page_size - 1) // page_size
+        folder, runtime = cpu_runtime(f"random{seed}", pages, page_size)
+    finally:
+        del bh.CONFIGS[f"random{seed}"]
+    session, outputs = TraceSession(runtime), {}
+    for record in steps:
+        outputs[record["step"]] = session.run(record).double()
+        runtime.manager.check_invariants()
+    got = helpers.collect(steps, outputs)
+    stored, weights = bh.load_folder(folder)
+    for rid, tokens in requests.items():
+        expected = plain.forward(tokens, weights, stored)
+        for position, row in got[rid].items():
+            assert torch.allclose(row, expected[position], atol=3e-4, rtol=3e-4), (seed, rid, position)
+
+
 def test_pages_behind_a_chunk_are_given_back():
     """A paged group under a chunked mask keeps the pages of the chunk that the next token lies in and gives back those
     wholly before it."""
