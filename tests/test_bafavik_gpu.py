@@ -559,7 +559,7 @@ _ORACLE: dict = {}
 
 
 def oracle(folder, tokens):
-    key = (str(folder), tuple(tokens))
+    key = (Path(folder).name, tuple(tokens))      # (a folder's name says configuration, seed and stored type: the same weights)
     if key not in _ORACLE:
         config, weights = bh.load_folder(folder)
         _ORACLE[key] = plain.forward(tokens, weights, config)
