@@ -7,6 +7,7 @@
 //
 // The block that handles a request's first token of the step reads the slot and then writes what the request's last token of
 // the step leaves there; no other block touches the slot, and the inputs are not written, so the order of blocks is free.
+// (The padding rows of a captured decode step all name the scratch slot and race for it; no request ever reads that slot.)
 #include "common.cuh"
 #include "elementwise_vec.cuh"
 

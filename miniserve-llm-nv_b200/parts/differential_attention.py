@@ -57,7 +57,8 @@ class DifferentialAttention(Part):
         self.general = True          # (what the report of attention kernels asks: the general call of paged_attention)
 
     @property
-    def num_q_maps(self) -> int:
+    def attention_heads(self) -> int:
+        """Query heads as the attention kernels see them: both maps of every head."""
         return 2 * self.num_heads
 
     def param_specs(self) -> list[ParamSpec]:
