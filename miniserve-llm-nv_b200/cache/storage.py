@@ -3,7 +3,8 @@ the sampling records of the state slots.
 
 A paged group's pools have the shape ``[runs, pages + 1, kv_heads, page_size, head_dim]`` for
 keys and the same for values (the layout of miniserve/kv/layout.py:65-75 per group; the last dimension of the
-value pool is the value head's size where the mixer's values are of another size than its keys); a group of
+value pool is the value head's size where the mixer's values are of another size than its keys, and its head count the
+number of value heads where several key heads share one); a group of
 latent vectors has one pool ``[runs, pages + 1, page_size, rank + rot]``; the last
 page is a scratch page that no request ever holds: padding rows of a replayed CUDA graph write
 to it.  State tensors and sampling records likewise have one slot more than there are requests,
@@ -39,7 +40,8 @@ class CacheStorage:
             if isinstance(need, PagedKVNeed):
                 shape = (group.n_slots, num_pages + 1, need.num_kv_heads, page_size)
                 self.key_pools.append(torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device))
-                self.value_pools.append(torch.zeros(shape + (need.value_head_dim,), dtype=dtype, device=device))
+                value_shape = (group.n_slots, num_pages + 1, need.num_value_heads, page_size, need.value_head_dim)
+                self.value_pools.append(torch.zeros(value_shape, dtype=dtype, device=device))
                 self.states.append(None)
                 self.paged_index.append(paged)
                 paged += 1
@@ -73,7 +75,7 @@ class CacheStorage:
     def bytes_per_page(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype) -> int:
         """Bytes one page number costs across all paged groups (keys and values or latent vectors, all runs)."""
         size = torch.empty((), dtype=dtype).element_size()
-        return (sum(g.n_slots * g.need.num_kv_heads * page_size * (g.need.head_dim + g.need.value_head_dim) * size
+        return (sum(g.n_slots * page_size * (g.need.num_kv_heads * g.need.head_dim + g.need.num_value_heads * g.need.value_head_dim) * size
                     for g in groups if isinstance(g.need, PagedKVNeed))
                 + sum(g.n_slots * page_size * (g.need.rank + g.need.rot) * size
                       for g in groups if isinstance(g.need, PagedLatentNeed)))

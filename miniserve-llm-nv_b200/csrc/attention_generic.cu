@@ -71,7 +71,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                const int* __restrict__ positions, int page_size, int n_q, int n_kv,
                                                int d, float scale, int window, float softcap,
                                                const float* __restrict__ bias_slopes, T* __restrict__ out, int dv,
-                                               int sink, const T* __restrict__ gate, int gate_ld, int chunk) {
+                                               int sink, const T* __restrict__ gate, int gate_ld, int chunk, int n_v) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float smem[];
@@ -104,10 +104,11 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
     const int key = block * 32 + lane;
     const bool valid = key >= first_key && key <= last_key;
     float score = -INFINITY;
-    size_t row_offset = 0;
+    size_t row_offset = 0, value_offset = 0;
     if (valid) {
       const int page = table[key / page_size];
-      row_offset = ((size_t)page * n_kv + kv_head) * page_size + key % page_size;      // the row's index in both pools
+      row_offset = ((size_t)page * n_kv + kv_head) * page_size + key % page_size;      // the row's index in the key pool
+      value_offset = ((size_t)page * n_v + kv_head % n_v) * page_size + key % page_size;      // and in the value pool (n_v heads)
       score = dot_row(q_s, k_pool + row_offset * d, d);
       if (softcap > 0.f) score = softcap * tanhf(score / softcap);
       score += slope * (float)(key - pos);
@@ -122,7 +123,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
     for (int i = 0; i < kMaxLanesPerThread; ++i) acc[i] *= correction;
     for (int j = 0; j < 32; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
-      const size_t off_j = __shfl_sync(0xffffffffu, (unsigned long long)row_offset, j);
+      const size_t off_j = __shfl_sync(0xffffffffu, (unsigned long long)value_offset, j);
       if (pj == 0.f) continue;   // uniform across the warp
       const T* v_row = v_pool + off_j * dv;
 #pragma unroll
@@ -170,12 +171,13 @@ using namespace ms;
 // [n_q] float32 or null.  dv: the size of a value head (value pool [pages, n_kv, page_size, dv], out [n_tokens, n_q, dv]);
 // sink != 0: one more term exp(0) in the softmax's denominator; gate (null: none): logits of the model's element type,
 // gate[token * gate_ld + head], whose sigmoid multiplies the head's output.  chunk > 0: a token sees only the keys of its own
-// chunk of `chunk` positions (position p: keys p - p % chunk .. p).
+// chunk of `chunk` positions (position p: keys p - p % chunk .. p).  n_v: the value pool holds that many heads, [pages, n_v,
+// page_size, dv] (a divisor of n_kv; key head g reads value head g % n_v: key heads that share values).
 MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k_pool, const void* v_pool,
                                          const int* block_tables, int table_stride, const int* request_of_token,
                                          const int* positions, int page_size, int n_q, int n_kv, int d, float scale,
                                          int window, float softcap, const float* bias_slopes, void* out, int n_tokens,
-                                         int dv, int sink, const void* gate, int gate_ld, int chunk, cudaStream_t stream) {
+                                         int dv, int sink, const void* gate, int gate_ld, int chunk, int n_v, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(d > 0 && d <= 32 * kMaxLanesPerThread, "paged_attention: head size %d outside 1..%d", d,
              32 * kMaxLanesPerThread);
@@ -184,6 +186,7 @@ MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k
   MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "paged_attention: %d query heads are not a multiple of %d key/value heads",
              n_q, n_kv);
   MS_REQUIRE(page_size > 0, "paged_attention: page size must be positive, got %d", page_size);
+  MS_REQUIRE(n_v > 0 && n_kv % n_v == 0, "paged_attention: %d value heads for %d key heads", n_v, n_kv);
   MS_REQUIRE(n_q <= 65535, "paged_attention: %d query heads exceed 65535", n_q);
   const size_t smem = (size_t)(d + kAttnWarps * dv + 2 * kAttnWarps) * sizeof(float);
   dim3 grid(n_tokens, n_q);
@@ -191,12 +194,12 @@ MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k
     ms::launch(paged_attention_generic_kernel<float>, grid, kAttnWarps * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, table_stride, request_of_token,
         positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes, (float*)out, dv, sink,
-        (const float*)gate, gate_ld, chunk);
+        (const float*)gate, gate_ld, chunk, n_v);
   } else if (dtype == MS_BF16) {
     ms::launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, kAttnWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_tables,
         table_stride, request_of_token, positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes,
-        (__nv_bfloat16*)out, dv, sink, (const __nv_bfloat16*)gate, gate_ld, chunk);
+        (__nv_bfloat16*)out, dv, sink, (const __nv_bfloat16*)gate, gate_ld, chunk, n_v);
   } else {
     MS_FAIL("paged_attention: unknown element type code %d", dtype);
   }

@@ -22,7 +22,7 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
                          int n_kv, int d, int dv, float scale_log2, int window, __nv_bfloat16* __restrict__ out,
                          float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits, int sink,
-                         const __nv_bfloat16* __restrict__ gate, int gate_ld, int chunk) {
+                         const __nv_bfloat16* __restrict__ gate, int gate_ld, int chunk, int n_v) {
   grid_dependency_wait();
   grid_dependency_launch();
   constexpr int BM = 16 * W, THREADS = 32 * W;
@@ -32,7 +32,8 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][ks]
   __nv_bfloat16* k_s = q_s + BM * ks;                                       // [2][BN][ks]
   __nv_bfloat16* v_s = k_s + 2 * BN * ks;                                   // [2][BN][vs]
-  long long* row_index = reinterpret_cast<long long*>(v_s + 2 * BN * vs);   // [2][BN] row of a key in the pools, -1: none
+  long long* row_index = reinterpret_cast<long long*>(v_s + 2 * BN * vs);   // [2][BN] row of a key in the key pool, -1: none
+  long long* value_index = row_index + 2 * BN;                              // [2][BN] its row in the value pool (n_v heads)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.y;
@@ -85,12 +86,14 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int key0 = tile_begin + tile * BN;
     for (int r = tid; r < BN; r += THREADS) {
       const int key = key0 + r;
-      long long index = -1;
+      long long index = -1, value = -1;
       if (tile < tile_hi && key < key_end) {
         const int page = table[key / page_size];
         index = ((long long)page * n_kv + kv_head) * page_size + key % page_size;
+        value = ((long long)page * n_v + kv_head % n_v) * page_size + key % page_size;
       }
       row_index[buffer * BN + r] = index;
+      value_index[buffer * BN + r] = value;
     }
   };
   auto load_tile = [&](int stage) {
@@ -102,9 +105,10 @@ attention_mma_any_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       const long long at = rows[r];
       cp_async_16(kt + r * ks + c * 8, k_pool + (at < 0 ? 0 : at * d + c * 8), at >= 0);
     }
+    const long long* value_rows = value_index + stage * BN;
     for (int i = tid; i < BN * v_chunks; i += THREADS) {
       const int r = i / v_chunks, c = i % v_chunks;
-      const long long at = rows[r];
+      const long long at = value_rows[r];
       cp_async_16(vt + r * vs + c * 8, v_pool + (at < 0 ? 0 : at * dv + c * 8), at >= 0);
     }
   };
@@ -281,13 +285,13 @@ int launch_attention_any(const void* q, const void* k_pool, const void* v_pool, 
                          const int* query_start, const int* context_lens, int page_size, int n_q, int n_kv, int d, int dv,
                          float scale, int window, void* out, float* part_o, float* part_lse, int num_splits, int n_requests,
                          int max_query_len, int n_tokens, int sink, const void* gate, int gate_ld, int first_token,
-                         int chunk, cudaStream_t stream) {
+                         int chunk, int n_v, cudaStream_t stream) {
   constexpr int BM = 16 * W;
-  const size_t smem = (size_t)(BM * (d + 8) + 2 * BN * (d + 8) + 2 * BN * (dv + 8)) * sizeof(__nv_bfloat16) + 2 * BN * sizeof(long long);
+  const size_t smem = (size_t)(BM * (d + 8) + 2 * BN * (d + 8) + 2 * BN * (dv + 8)) * sizeof(__nv_bfloat16) + 4 * BN * sizeof(long long);
   auto kernel = attention_mma_any_kernel<W, BN>;
   static bool configured = false;
   if (!configured) {
-    const size_t most = (size_t)(BM + 4 * BN) * (kAnyMax + 8) * sizeof(__nv_bfloat16) + 2 * BN * sizeof(long long);
+    const size_t most = (size_t)(BM + 4 * BN) * (kAnyMax + 8) * sizeof(__nv_bfloat16) + 4 * BN * sizeof(long long);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
     if (e != cudaSuccess) MS_FAIL("attention (any head size): cannot reserve %zu bytes of shared memory: %s", most, cudaGetErrorString(e));
     configured = true;
@@ -299,7 +303,7 @@ int launch_attention_any(const void* q, const void* k_pool, const void* v_pool, 
   dim3 grid((unsigned)tiles, n_kv, n_requests * num_splits);
   ms::launch(kernel, grid, W * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
              block_tables, table_stride, query_start, context_lens, page_size, n_q, n_kv, d, dv, scale * 1.4426950408889634f, window,
-             (__nv_bfloat16*)out, part_o, part_lse, num_splits, sink, (const __nv_bfloat16*)gate, gate_ld, chunk);
+             (__nv_bfloat16*)out, part_o, part_lse, num_splits, sink, (const __nv_bfloat16*)gate, gate_ld, chunk, n_v);
   MS_CHECK_LAUNCH("attention_mma_any");
   if (num_splits > 1) {
     const size_t skip = (size_t)first_token * n_q;
@@ -336,24 +340,26 @@ MS_EXPORT int ms_attention_mma_any_splits(int n_requests, int n_kv, int n_q, int
 }
 
 // Arguments as ms_paged_attention_mma, with the value heads' size dv: q [n_tokens, n_q, d], key pool [pages, n_kv, page_size, d],
-// value pool [pages, n_kv, page_size, dv], out [n_tokens, n_q, dv]; part_o [n_tokens * n_q * num_splits * dv].
+// value pool [pages, n_v, page_size, dv] (n_v a divisor of n_kv: key head g reads value head g % n_v), out [n_tokens, n_q, dv];
+// part_o [n_tokens * n_q * num_splits * dv].
 MS_EXPORT int ms_paged_attention_mma_any(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                          int table_stride, const int* query_start, const int* context_lens, int page_size,
                                          int n_q, int n_kv, int d, int dv, float scale, int window, void* out, float* part_o,
                                          float* part_lse, int num_splits, int n_requests, int max_query_len, int n_tokens,
-                                         int sink, const void* gate, int gate_ld, int first_token, int chunk, cudaStream_t stream) {
+                                         int sink, const void* gate, int gate_ld, int first_token, int chunk, int n_v, cudaStream_t stream) {
   if (n_tokens == 0 || n_requests == 0) return 0;
   MS_REQUIRE(ms_attention_mma_any_supports(d, dv), "attention (any head size): sizes %d and %d are not multiples of 16 up to %d", d, dv, kAnyMax);
   MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d query heads are not a multiple of %d key/value heads", n_q, n_kv);
   MS_REQUIRE(page_size > 0 && max_query_len > 0, "attention: page size %d, longest portion %d", page_size, max_query_len);
   MS_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || (part_o && part_lse)), "attention: %d splits (1..64) need scratch", num_splits);
   MS_REQUIRE(first_token >= 0 && first_token < n_tokens, "attention: first row %d of %d", first_token, n_tokens);
+  MS_REQUIRE(n_v > 0 && n_kv % n_v == 0, "attention: %d value heads for %d key heads", n_v, n_kv);
   const bool small = (long long)max_query_len * (n_q / n_kv) <= 16;
   if (small)
     return launch_attention_any<1, 32>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens, page_size, n_q, n_kv, d,
                                        dv, scale, window, out, part_o, part_lse, num_splits, n_requests, max_query_len, n_tokens, sink,
-                                       gate, gate_ld, first_token, chunk, stream);
+                                       gate, gate_ld, first_token, chunk, n_v, stream);
   return launch_attention_any<4, 64>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens, page_size, n_q, n_kv, d, dv,
                                      scale, window, out, part_o, part_lse, num_splits, n_requests, max_query_len, n_tokens, sink, gate,
-                                     gate_ld, first_token, chunk, stream);
+                                     gate_ld, first_token, chunk, n_v, stream);
 }

@@ -140,7 +140,8 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, co
 // entry 2i + 1); the pair (u, v)
 // becomes (u cos - v sin, v cos + u sin) with (cos, sin) = cos_sin[n, i].  A negative slot skips the writes.
 // bias (null: none): float32 [ld], the projection's bias column by column, added in float32 to every head as it is read.
-// value_heads: the projection holds that many value heads (a divisor of n_kv); the pool's value head g is head g % value_heads.
+// value_heads: the projection and the value pool [page, value_heads, page_size, dv] hold that many value heads (a divisor of
+// n_kv: key heads that share values).
 template <typename T>
 __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv,
                                    int d, int dv, const int* __restrict__ slots, const float* __restrict__ q_weight,
@@ -153,7 +154,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col
   extern __shared__ float prepare_smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads = n_q + (k_col >= 0 ? 2 * n_kv : 0);
+  const int heads = n_q + (k_col >= 0 ? n_kv + value_heads : 0);
   const long long item = (long long)blockIdx.x * warps_per_block + warp;
   if (item >= (long long)n_tokens * heads) return;
   const int n = (int)(item / heads), head = (int)(item % heads);
@@ -173,10 +174,10 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col
     const int page = slot / page_size, offset = slot % page_size;
     if (head >= n_q + n_kv) {
       const int g = head - n_q - n_kv;
-      src = row + v_col + (g % value_heads) * dv;        // (fewer projected value heads than key heads: they repeat)
-      dst = v_pool + (((size_t)page * n_kv + g) * page_size + offset) * dv;
+      src = row + v_col + g * dv;                        // (value_heads of them: key head g reads value head g % value_heads)
+      dst = v_pool + (((size_t)page * value_heads + g) * page_size + offset) * dv;
       if (bias) {
-        const float* b = bias + v_col + (g % value_heads) * dv;
+        const float* b = bias + v_col + g * dv;
         for (int c = lane; c < dv; c += 32) dst[c] = from_float<T>(to_float(src[c]) + b[c]);
       } else {
         for (int c = lane; c < dv; c += 32) dst[c] = src[c];
@@ -272,13 +273,13 @@ MS_EXPORT int ms_qkv_prepare(const void* proj, int dtype, int ld, int q_col, int
   MS_REQUIRE(k_col < 0 || (v_col >= 0 && slots && k_pool && v_pool), "qkv_prepare: keys and values need their columns, slots and pools");
   MS_REQUIRE(k_col < 0 || (value_heads >= 1 && n_kv % value_heads == 0), "qkv_prepare: %d value heads for %d key heads", value_heads, n_kv);
   const int warps = 4;
-  const long long items = (long long)n_tokens * (n_q + (k_col >= 0 ? 2 * n_kv : 0));
+  const long long items = (long long)n_tokens * (n_q + (k_col >= 0 ? n_kv + (value_heads > 0 ? value_heads : n_kv) : 0));
   const long long blocks = (items + warps - 1) / warps;
   MS_REQUIRE(blocks < 2147483647LL, "qkv_prepare: %lld heads in one launch is too many", items);
   const size_t smem = (size_t)warps * d * sizeof(float);
   MS_EG_DISPATCH(dtype, (ms::launch(qkv_prepare_kernel<T>, (unsigned)blocks, warps * 32, smem, stream, (const T*)proj, ld, q_col,
                                     k_col, v_col, n_q, n_kv, d, dv, slots, q_weight, k_weight, eps, (const float2*)cos_sin,
-                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens, interleaved, bias, value_heads > 0 ? value_heads : 1)));
+                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens, interleaved, bias, value_heads > 0 ? value_heads : n_kv)));
   MS_CHECK_LAUNCH("qkv_prepare");
   return 0;
 }

@@ -140,7 +140,7 @@ def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size
         n_q = getattr(mixer, "attention_heads", None) or getattr(mixer, "num_heads", need.num_kv_heads)
         modified = bool(getattr(mixer, "score_softcap", None)) or getattr(mixer, "score_bias_slopes", None) is not None
         names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size, modified, need.value_dim,
-                                          bool(getattr(mixer, "general", False)), need.chunk)
+                                          bool(getattr(mixer, "general", False)), need.chunk, need.num_value_heads != need.num_kv_heads)
         chosen.append(dict(group=plan.group, head_dim=need.head_dim, window=need.window, **names))
         slow = dtype == torch.bfloat16 and "general" in names.values()
         log.log(logging.WARNING if slow else logging.INFO,

@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -195,8 +195,8 @@ def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int
     [N, n_q, head_dim]`` is written.  Key pool ``[pages, n_kv, page_size, head_dim]``, value pool ``[.., value_dim]``;
     norm weights float32 ``[head_dim]`` or None; ``cos_sin`` float32 ``[N, rotary_dim / 2, 2]`` or None.  ``bias`` (float32
     ``[ld]``, column by column as ``proj``): the projection's bias, added in float32 as the heads are read.  ``value_heads``
-    (a divisor of ``n_kv``; None: ``n_kv``): the projection holds that many value heads, and the pool's value head g receives
-    head ``g % value_heads`` (key heads that share values)."""
+    (a divisor of ``n_kv``; None: ``n_kv``): the projection and the value pool ``[pages, value_heads, page_size, value_dim]`` hold
+    that many value heads (key heads that share values: key head g reads value head ``g % value_heads``)."""
     n, ld = proj.shape
     value_heads = n_kv if value_heads is None else int(value_heads)
     if value_heads < 1 or n_kv % value_heads:
@@ -213,8 +213,9 @@ def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int
         _want(k_pool, "k_pool", proj.dtype)
         _want(v_pool, "v_pool", proj.dtype)
         if (k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, k_pool.shape[2], head_dim)
-                or tuple(v_pool.shape) != tuple(k_pool.shape[:3]) + (value_dim,)):
-            raise KernelError(f"pool shapes {tuple(k_pool.shape)}, {tuple(v_pool.shape)} are not [pages, {n_kv}, page_size, {head_dim} | {value_dim}]")
+                or tuple(v_pool.shape) != (k_pool.shape[0], value_heads, k_pool.shape[2], value_dim)):
+            raise KernelError(f"pool shapes {tuple(k_pool.shape)}, {tuple(v_pool.shape)} are not [pages, {n_kv} | {value_heads}, page_size, "
+                              f"{head_dim} | {value_dim}]")
     for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
         if weight is not None:
             _want(weight, name, torch.float32, (head_dim,))
@@ -406,13 +407,14 @@ USE_MMA_ANY = __import__("os").environ.get("MINISERVE_B200_MMA_ANY", "1") == "1"
 
 def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, page_size: int,
                       modified_scores: bool = False, value_dim: Optional[int] = None, extended: bool = False,
-                      chunk: Optional[int] = None) -> dict:
+                      chunk: Optional[int] = None, shared_values: bool = False) -> dict:
     """Which kernel :func:`paged_attention` runs for these sizes: ``{"decode": name, "prompt": name}`` with the
     names ``tcgen05``, ``mma.sync`` and ``general`` (float32 arithmetic, any size; the only one of the float32
     path, and what bfloat16 falls back to for head sizes the tensor-core kernels are not built for and for
     scores with a soft cap or a distance bias)."""
     lib = library()
     value_dim = head_dim if value_dim is None else value_dim
+    chunk = chunk or (1 if shared_values else None)      # (key heads that share value heads: the same two kernels)
     extended = extended or bool(chunk)
     if (USE_MMA_ANY and extended and not modified_scores and dtype == torch.bfloat16
             and (value_dim != head_dim or bool(chunk) or not lib.ms_attention_mma_supports(_i(head_dim)))
@@ -437,7 +439,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     """Causal grouped-query attention of every token over its request's paged keys and values.
 
     ``chunk``: a token at position p sees only the keys of its own chunk, ``p - p % chunk .. p`` (chunks are counted from
-    position 0 of the sequence).  The general kernel and the tensor-core kernel for any head size implement it.
+    position 0 of the sequence).  A value pool with fewer heads than the key pool (a divisor): key head g reads value head
+    ``g % value heads``.  The general kernel and the tensor-core kernel for any head size implement both.
 
     q ``[N, n_q, d]``, out ``[N, n_q, dv]`` (dv: the value pool's last dimension, usually d); pools of one layer
     ``[pages, n_kv, page_size, d | dv]``.  ``sink``: the softmax's denominator gets one more term ``exp(0)`` (a key of
@@ -466,9 +469,10 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if k_pool.dim() != 4 or k_pool.shape[3] != head_dim:
         raise KernelError(f"pool shape {tuple(k_pool.shape)} is not [pages, n_kv, page_size, {head_dim}]")
     _want(v_pool, "v_pool", q.dtype)
-    if v_pool.dim() != 4 or v_pool.shape[:3] != k_pool.shape[:3]:
+    if (v_pool.dim() != 4 or v_pool.shape[0] != k_pool.shape[0] or v_pool.shape[2] != k_pool.shape[2]
+            or v_pool.shape[1] < 1 or k_pool.shape[1] % v_pool.shape[1]):
         raise KernelError(f"value pool {tuple(v_pool.shape)} does not go with key pool {tuple(k_pool.shape)}")
-    value_dim = v_pool.shape[3]
+    value_dim, n_v = v_pool.shape[3], v_pool.shape[1]
     _want(out, "out", q.dtype, (n, n_q, value_dim))
     gate_ptr, gate_ld = None, 0
     if gate is not None:
@@ -489,9 +493,10 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _want(bias_slopes, "bias_slopes", torch.float32, (n_q,))
     # the general form (a sink, a gate, value heads of their own size) at sizes the unrolled tensor-core kernels are not built
     # for: the tensor-core kernel whose head sizes are run-time numbers (multiples of 16 up to 128)
-    extended = sink or gate is not None or value_dim != head_dim or bool(chunk)
+    shared_values = n_v != n_kv
+    extended = sink or gate is not None or value_dim != head_dim or bool(chunk) or shared_values
     if (USE_MMA_ANY and extended and not modified and q.dtype == torch.bfloat16
-            and (value_dim != head_dim or bool(chunk) or not lib.ms_attention_mma_supports(_i(head_dim)))
+            and (value_dim != head_dim or bool(chunk) or shared_values or not lib.ms_attention_mma_supports(_i(head_dim)))
             and lib.ms_attention_mma_any_supports(_i(head_dim), _i(value_dim))):
         reach = min(max_context_len, chunk) if chunk else max_context_len      # the most keys a token sees
         def run_any(first: int, last: int, longest: int, rows: int, first_row: int = 0) -> None:
@@ -506,7 +511,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 _ptr(query_start[first:last + 1]), _ptr(context_lens[first:last]), _i(k_pool.shape[2]), _i(n_q), _i(n_kv),
                 _i(head_dim), _i(value_dim), _f(scale), _i(window if window else 0), _ptr(out), _ptr(part_o), _ptr(part_lse),
                 _i(splits), _i(count), _i(longest), _i(rows), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(first_row),
-                _i(chunk or 0), _stream()))
+                _i(chunk or 0), _i(n_v), _stream()))
 
         single = 0
         if host_query_start and max_query_len > 1 and len(host_query_start) == n_requests + 1:
@@ -518,13 +523,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         else:
             run_any(0, n_requests, max_query_len, n)
         return
-    general = modified or value_dim != head_dim or bool(chunk)      # (the unrolled tensor-core kernels take the sink and the gate, not these)
+    general = modified or value_dim != head_dim or bool(chunk) or shared_values      # (the unrolled tensor-core kernels take the sink and the gate, not these)
     if general or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         _check(lib.ms_paged_attention_generic(
             _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
             _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim),
             _f(scale), _i(window if window else 0), _f(softcap if softcap else 0.0), _ptr(bias_slopes), _ptr(out),
-            _i(n), _i(value_dim), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(chunk or 0), _stream()))
+            _i(n), _i(value_dim), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(chunk or 0), _i(n_v), _stream()))
         return
 
     def run(first: int, last: int, longest: int, rows: int, first_row: int = 0) -> None:

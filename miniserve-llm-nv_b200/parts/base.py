@@ -59,13 +59,20 @@ class ParamSpec:
 class PagedKVNeed:
     """The mixer keeps keys and values per token in pages; ``window`` keys back at most (None: all).  ``value_dim``:
     the size of a value head where it differs from the size of a key head (None: the same).  ``chunk``: a token sees only
-    the keys of its own chunk of that many positions, counted from position 0 (None: no chunks)."""
+    the keys of its own chunk of that many positions, counted from position 0 (None: no chunks).  ``value_heads``: the number
+    of value heads where several key heads share one (a divisor of ``num_kv_heads``; key head g reads value head
+    ``g % value_heads``; None: one per key head)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
     chunk: Optional[int] = None
+    value_heads: Optional[int] = None
+
+    @property
+    def num_value_heads(self) -> int:
+        return self.num_kv_heads if self.value_heads is None else self.value_heads
 
     @property
     def value_head_dim(self) -> int:

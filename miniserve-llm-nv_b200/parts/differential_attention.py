@@ -9,10 +9,10 @@ Options: biases on q, k and v (added in float32 as the heads are read), a positi
 sees only the keys of its own chunk of that many positions, counted from position 0 of the sequence.
 
 How it runs: at load the rows of ``W_q`` and ``W_k`` are reordered so that all first-map heads come before all second-map
-heads.  The layer is then an ordinary grouped-query attention of ``2 H`` query heads over ``2 G`` key heads, for which the
-engine's paged attention kernels are used as they are; the values are projected once and written for both halves of the key
-heads (the value rows of the projection are read twice), so the cache of such a layer holds ``2 G`` key heads and as many
-value heads.  One kernel then combines the two halves of the output, norms, scales and gates.
+heads.  The layer is then an ordinary grouped-query attention of ``2 H`` query heads over ``2 G`` key heads whose two halves
+share ``G`` value heads (key head g reads value head ``g % G``: ``PagedKVNeed.value_heads``), for which the engine's paged
+attention kernels are used; the cache of such a layer holds ``2 G`` key heads and ``G`` value heads.  One kernel then combines
+the two halves of the output, norms, scales and gates.
 """
 
 from __future__ import annotations
@@ -75,7 +75,7 @@ class DifferentialAttention(Part):
 
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(2 * self.num_kv_heads, self.head_dim, self.window,
-                           None if self.value_dim == self.head_dim else self.value_dim, self.chunk)
+                           None if self.value_dim == self.head_dim else self.value_dim, self.chunk, self.num_kv_heads)
 
     @staticmethod
     def _maps_apart(rows: torch.Tensor, heads: int, d: int) -> torch.Tensor:
@@ -106,7 +106,7 @@ class DifferentialAttention(Part):
         kernels.linear(x, self.in_weight, proj)
         cos_sin, rotary_dim, interleaved = self.position.fused_args(ctx)
         q = ctx.buffer("differential_attention.q", (n, 2 * H, d), x.dtype)
-        # first-map keys with the values, then second-map keys with the same values
+        # first-map keys, then second-map keys; both halves read the same G value heads
         key_pool, value_pool = cache.key_pool, cache.value_pool
         kernels.qkv_prepare(proj, 0, self.k_col, self.v_col, 2 * H, 2 * G, d, dv, cache.slots, None, None, self.eps, cos_sin,
                             rotary_dim, key_pool, value_pool, q, interleaved=interleaved, bias=self.in_bias, value_heads=G)

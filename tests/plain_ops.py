@@ -156,7 +156,8 @@ def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions
         pages = table[(keys // page_size).long()].long()
         offsets = (keys % page_size).long()
         k = k_pool[pages, :, offsets, :].double()      # [keys, n_kv, d]
-        v = v_pool[pages, :, offsets, :].double()
+        v = v_pool[pages, :, offsets, :].double()      # [keys, value heads, dv]
+        n_v = v.shape[1]
         for head in range(n_q):
             scores = (k[:, head // group, :] @ q[token, head].double()) * scale
             if softcap:
@@ -169,7 +170,7 @@ def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions
                 p = e / (e.sum() + torch.exp(-top))
             else:
                 p = torch.softmax(scores, dim=0)
-            result = p @ v[:, head // group, :]
+            result = p @ v[:, (head // group) % n_v, :]
             if gate is not None:
                 result = result * torch.sigmoid(gate[token, gate_col + head].double())
             out[token, head] = result.to(out.dtype)
@@ -385,7 +386,7 @@ def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots
         return
     k = heads(k_col, n_kv, head_dim, k_weight)
     value_heads = n_kv if value_heads is None else value_heads
-    v = proj[:, v_col:v_col + value_heads * value_dim].view(n, value_heads, value_dim).repeat(1, n_kv // value_heads, 1)
+    v = proj[:, v_col:v_col + value_heads * value_dim].view(n, value_heads, value_dim)
     page_size = k_pool.shape[2]
     for token in range(n):
         slot = int(slots[token])

@@ -41,7 +41,8 @@ def test_configuration_reads_every_size_and_round_trips():
             shift_groups.add(own.group)
             if entry["type"] == "attention":
                 need = model.cache_groups[inner.group].need
-                assert need == PagedKVNeed(2 * m["kv_heads"], m["dim"], None, None if m["vdim"] == m["dim"] else m["vdim"], m["mask"]["size"])
+                assert need == PagedKVNeed(2 * m["kv_heads"], m["dim"], None, None if m["vdim"] == m["dim"] else m["vdim"], m["mask"]["size"],
+                                           m["kv_heads"])          # both maps' key heads over ONE set of value heads
                 assert names[p + "q"].shape == (m["heads"] * 2 * m["dim"], width) and names[p + "g"].shape == (m["heads"] * m["vdim"], width)
                 assert names[p + "lk2"].shape == (m["dim"],) and names[p + "k.b"].shape == (m["kv_heads"] * 2 * m["dim"],)
             elif entry["type"] == "parallel":

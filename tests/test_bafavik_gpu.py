@@ -268,7 +268,7 @@ def test_prepare_with_biases_and_shared_values_and_convolution_in_the_compute_ty
     cos_sin = torch.empty((n, 3, 2)).cuda()
     kernels.rope_table(ints(list(range(3, 3 + n))), torch.tensor([1.0, 0.1, 0.01]).cuda(), cos_sin)
     slots = ints([9, 2, -1, 0, 5, 6, 7])
-    pools = [torch.zeros((3, n_kv, page, size), dtype=dtype).cuda() for size in (d, dv)]
+    pools = [torch.zeros((3, heads, page, size), dtype=dtype).cuda() for heads, size in ((n_kv, d), (n_v, dv))]
     want_pools = [cpu(p) for p in pools]
     q, want_q = torch.empty((n, n_q, d), dtype=dtype).cuda(), torch.empty((n, n_q, d), dtype=dtype)
     ones = torch.ones(d).cuda()
@@ -277,7 +277,7 @@ def test_prepare_with_biases_and_shared_values_and_convolution_in_the_compute_ty
     plain_ops.qkv_prepare(cpu(proj), 0, n_q * d, (n_q + n_kv) * d, n_q, n_kv, d, dv, cpu(slots), cpu(ones), cpu(ones), 1e-5, cpu(cos_sin), 6,
                           want_pools[0], want_pools[1], want_q, interleaved=True, bias=cpu(bias), value_heads=n_v)
     assert close(q, want_q, dtype, 2.0) and close(pools[0], want_pools[0], dtype, 2.0) and close(pools[1], want_pools[1], dtype, 2.0)
-    assert torch.equal(pools[1][:, :2], pools[1][:, 2:]) and float(pools[1].abs().max()) > 0      # key heads 0, 2 and 1, 3 share values
+    assert float(pools[1].abs().max()) > 0             # (two value heads for four key heads: key heads 0, 2 and 1, 3 share them)
     # the convolution's results in the projection's own type
     channels, taps = 35, 4
     weight, states = rand((channels, taps), torch.float32, 3, 0.6), rand((2, 3 * channels), torch.float32, 4)
@@ -289,12 +289,14 @@ def test_prepare_with_biases_and_shared_values_and_convolution_in_the_compute_ty
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n_q,n_kv,d,dv,chunk,page", [(6, 2, 48, 80, 100, 16), (4, 4, 32, 64, 50, 8), (2, 2, 12, 20, 13, 8), (10, 10, 6, 6, 1, 4),
-                                                        (4, 2, 64, 64, 37, 16), (2, 1, 128, 32, 200, 64)])
-def test_attention_kernels_under_a_chunked_mask(dtype, n_q, n_kv, d, dv, chunk, page):
+@pytest.mark.parametrize("n_q,n_kv,n_v,d,dv,chunk,page", [(6, 2, 1, 48, 80, 100, 16), (4, 4, 4, 32, 64, 50, 8), (2, 2, 1, 12, 20, 13, 8),
+                                                            (10, 10, 5, 6, 6, 1, 4), (4, 2, 2, 64, 64, 37, 16), (2, 1, 1, 128, 32, 200, 64),
+                                                            (8, 4, 2, 64, 64, None, 16), (6, 6, 2, 10, 7, None, 8)])
+def test_attention_kernels_under_a_chunked_mask(dtype, n_q, n_kv, n_v, d, dv, chunk, page):
     """A prompt portion that crosses chunk borders beside single tokens just before, at and just behind a border, over pages
     in scrambled order: the general kernel (float32, and sizes no tensor-core kernel takes) and the tensor-core kernel for any
-    head size."""
+    head size.  Value pools of fewer heads than the key pool (key head g reads value head g % n_v), with and without chunks."""
+    masked, chunk = chunk, chunk or 40
     from miniserve_b200 import kernels
 
     contexts, queries = [2 * chunk + 3, chunk, chunk + 1, 3 * chunk - 1 if chunk > 1 else 5, 1], [min(2 * chunk + 3, chunk + 7), 1, 1, 1, 1]
@@ -307,18 +309,24 @@ def test_attention_kernels_under_a_chunked_mask(dtype, n_q, n_kv, d, dv, chunk, 
     for r, count in enumerate(pages_each):
         tables[r, :count] = torch.tensor(order[at:at + count], dtype=torch.int32)
         at += count
-    k_pool, v_pool = rand((total_pages, n_kv, page, d), dtype, 2), rand((total_pages, n_kv, page, dv), dtype, 3)
+    k_pool, v_pool = rand((total_pages, n_kv, page, d), dtype, 2), rand((total_pages, n_v, page, dv), dtype, 3)
     n = sum(queries)
     q = rand((n, n_q, d), dtype, 4)
     positions = [p for c, m in zip(contexts, queries) for p in range(c - m, c)]
     out, want = torch.empty((n, n_q, dv), dtype=dtype).cuda(), torch.empty((n, n_q, dv), dtype=torch.float64)
     host_starts = [sum(queries[:i]) for i in range(len(queries) + 1)]
     kernels.paged_attention(q, k_pool, v_pool, tables.cuda(), requests_of(queries), ints(positions), starts_of(queries), ints(contexts),
-                            max(queries), max(contexts), 0.3, None, out, host_starts, chunk=chunk)
+                            max(queries), max(contexts), 0.3, None, out, host_starts, chunk=masked)
     plain_ops.paged_attention(cpu(q), cpu(k_pool), cpu(v_pool), tables, cpu(requests_of(queries)), torch.tensor(positions), None, None,
-                              max(queries), max(contexts), 0.3, None, want, chunk=chunk)
+                              max(queries), max(contexts), 0.3, None, want, chunk=masked)
     assert close(out, want, dtype, float(want.abs().max()))
-    if chunk > 1:       # what the comparison rests on: another chunk size gives other rows
+    if n_v != n_kv:       # the value heads are shared as g % n_v, not as g // (n_kv / n_v)
+        other = torch.empty_like(want)
+        swapped = cpu(v_pool)[:, [(g // (n_kv // n_v)) for g in range(n_kv)]]
+        plain_ops.paged_attention(cpu(q), cpu(k_pool), swapped, tables, cpu(requests_of(queries)), torch.tensor(positions), None, None,
+                                  max(queries), max(contexts), 0.3, None, other, chunk=masked)
+        assert n_v == 1 or float((other - want).abs().max()) > 0.05 * float(want.abs().max())
+    if masked and chunk > 1:       # what the comparison rests on: another chunk size gives other rows
         other = torch.empty_like(want)
         plain_ops.paged_attention(cpu(q), cpu(k_pool), cpu(v_pool), tables, cpu(requests_of(queries)), torch.tensor(positions), None, None,
                                   max(queries), max(contexts), 0.3, None, other, chunk=chunk + 1)
