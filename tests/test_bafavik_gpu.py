@@ -574,7 +574,7 @@ def oracle(folder, tokens):
     return _ORACLE[key]
 
 
-def judge(ratios, dtype):
+def within_bounds(ratios, dtype):
     """``ratios``: (error / bound, where) of every position.  float32: all within the bound.  bfloat16: three positions in a
     hundred (one at least) may lie over it, none over four times it: where the two maps of a differential head nearly cancel,
     or a read-out of the delta rule does, the head's norm magnifies the rounding of what went in (the float32 path, which runs
@@ -597,7 +597,7 @@ def check(folder, dtype, requests, got, positions_of=None, slack=1.0):
         assert sorted(got[rid]) == list(wanted), rid
         for position, row in got[rid].items():
             ratios.append((float((row - expected[position]).abs().max()) / bound, (rid, position)))
-    return judge(ratios, dtype)
+    return within_bounds(ratios, dtype)
 
 
 CUTTINGS = {
@@ -661,7 +661,7 @@ def test_prefill_against_decoding_every_token(tmp_path, dtype, name):
     expected = oracle(folder, tokens)
     bound = bound_of(dtype, expected)
     for a, b in ((whole, expected), (single, expected), (single, whole)):
-        judge([(float((a[position] - b[position]).abs().max()) / bound, position) for position in range(len(tokens))], dtype)
+        within_bounds([(float((a[position] - b[position]).abs().max()) / bound, position) for position in range(len(tokens))], dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
